@@ -1,0 +1,475 @@
+"""Benchmark of the paged-KV attention hot path on B200.
+
+Default workload (N=1): decode attention at scale — batch 64, 48 query / 8 KV
+heads, head_dim 128, bf16 cache, contexts log-uniform in [4096, 32768], page 256
+with random physical placement, global (full-context) layer.  One step = one pass
+of decode attention over the batch for one layer.  With ``--gpus N`` the KV heads
+are sharded over N ranks (8/N KV heads and 48/N query heads per GPU, same
+sequences and block table on every rank) and no data-path collective is needed.
+
+Prints ONE JSON line: metric ``decode_attn_hbm_gbs`` = algorithmic KV+q+out bytes
+per step over all ranks divided by the device time of a step (max over ranks).
+
+``--impl reference`` times the CPU restatement of the reference path (the oracle;
+the reference itself has no CPU path and its attention kernel does not run on
+this GPU) on the host cores, on a bounded sample of the same workload.
+
+Other workloads (``--workload``) are for profiling: ``decode_local`` (window
+8192), ``prefill`` / ``prefill_local`` (chunked prefill, 8 x 2048-token chunks
+with cached prefixes), ``small`` (a short decode case for profiler captures).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+HQ, HKV, D, PAGE = 48, 8, 128, 256
+WINDOW_LOCAL = 8191
+L2_BYTES = 126 * 1024 * 1024
+
+
+# ------------------------------------------------------------------ workloads
+def decode_lengths(batch: int, lo: int, hi: int, seed: int) -> list[int]:
+    g = torch.Generator().manual_seed(seed)
+    u = torch.empty(batch).uniform_(math.log(lo), math.log(hi), generator=g)
+    return [int(round(math.exp(v))) for v in u.tolist()]
+
+
+def make_tables(kv_lens: list[int], seed: int) -> tuple[torch.Tensor, int]:
+    """Block table with random physical page placement; unused entries are 0."""
+    g = torch.Generator().manual_seed(seed)
+    pages = [(n + PAGE - 1) // PAGE for n in kv_lens]
+    n_pages = sum(pages)
+    perm = torch.randperm(n_pages, generator=g)
+    table = torch.zeros(len(kv_lens), max(pages), dtype=torch.int32)
+    ofs = 0
+    for b, npg in enumerate(pages):
+        table[b, :npg] = perm[ofs : ofs + npg].to(torch.int32)
+        ofs += npg
+    return table, n_pages
+
+
+def attended(ctx: int, window_left: int) -> int:
+    return ctx if window_left < 0 else min(ctx, window_left + 1)
+
+
+def decode_bytes(kv_lens: list[int], window_left: int, hq: int, hkv: int) -> int:
+    """Algorithmic bytes of one decode-attention pass: attended K and V rows, the
+    query and output rows, and the block-table entries and lengths read."""
+    kv = sum(attended(n, window_left) for n in kv_lens) * 2 * hkv * D * 2
+    qo = len(kv_lens) * hq * D * 2 * 2
+    meta = sum((attended(n, window_left) + PAGE - 1) // PAGE for n in kv_lens) * 4 + 8 * len(kv_lens)
+    return kv + qo + meta
+
+
+def prefill_pairs(seq_info: list[tuple[int, int]], window_left: int) -> int:
+    total = 0
+    for n0, n1 in seq_info:
+        if window_left < 0:
+            total += sum(range(n0 + 1, n0 + n1 + 1))
+        else:
+            w = window_left + 1
+            total += sum(min(p + 1, w) for p in range(n0, n0 + n1))
+    return total
+
+
+class ClockSampler:
+    """Polls nvidia-smi for SM clocks and throttle reasons while a region runs."""
+
+    FIELDS = (
+        "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+        "clocks_event_reasons.sw_power_cap"
+    )
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread: threading.Thread | None = None
+
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                     "--format=csv,noheader,nounits"],
+                    capture_output=True, text=True, timeout=5,
+                ).stdout.strip()
+                if out:
+                    self.samples.append([v.strip() for v in out.splitlines()[0].split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self) -> "ClockSampler":
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=10)
+
+    def summary(self) -> dict:
+        sm = [float(s[0]) for s in self.samples if s and s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if len(s) > 1 and s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [
+            n for i, n in enumerate(names)
+            if any(len(s) > 3 + i and s[3 + i].lower().startswith("active") for s in self.samples)
+        ]
+        return {
+            "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_max_mhz": max(mx) if mx else None,
+            "reasons": reasons,
+            "samples": len(self.samples),
+        }
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+# ---------------------------------------------------------------- CPU baseline
+def cpu_decode_baseline(kv_lens, table, cache_rows_fn, window_left, hq, hkv, budget_s, seed):
+    """Times the oracle's attention on whole sequences of the workload until about
+    ``budget_s`` seconds of CPU work are spent.  ``cache_rows_fn(pages)`` returns
+    the cache rows of the given physical pages as a CPU tensor."""
+    from oracle import ref_paged_gqa_attention
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(seed)
+    spent, done_bytes, used = 0.0, 0, 0
+    for b, n in enumerate(kv_lens):
+        npg = (n + PAGE - 1) // PAGE
+        pages = table[b, :npg].long()
+        rows = cache_rows_fn(pages)  # [npg * PAGE, hkv * 2 * D] bf16, local page order
+        k, v = torch.split(rows, [hkv * D, hkv * D], dim=1)
+        local_tbl = torch.arange(npg, dtype=torch.int32)[None]
+        q = torch.randn(1, hq, D, generator=g).to(torch.bfloat16)
+        t0 = time.perf_counter()
+        ref_paged_gqa_attention(
+            q, k.reshape(-1, PAGE, hkv, D), v.reshape(-1, PAGE, hkv, D),
+            torch.tensor([0, 1], dtype=torch.int32), torch.tensor([n], dtype=torch.int32),
+            local_tbl, D**-0.5, window_left,
+        )
+        spent += time.perf_counter() - t0
+        done_bytes += decode_bytes([n], window_left, hq, hkv)
+        used += 1
+        if spent >= budget_s:
+            break
+    return {
+        "value": done_bytes / spent / 1e9,
+        "unit": "GB/s",
+        "cores": torch.get_num_threads(),
+        "kind": "port",
+        "sample": f"{used} of {len(kv_lens)} sequences of the workload, whole contexts, "
+                  f"fp32 PyTorch restatement, {spent:.1f} s of CPU time",
+    }
+
+
+# ------------------------------------------------------------------------ main
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="decode_global",
+                    choices=["decode_global", "decode_local", "small", "prefill", "prefill_local"])
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    n_gpus = args.gpus
+    if world != n_gpus and world > 1:
+        raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}")
+    if HKV % n_gpus != 0:
+        raise SystemExit("--gpus must divide the 8 KV heads")
+
+    window_left = WINDOW_LOCAL if args.workload.endswith("local") else -1
+    if args.workload.startswith("prefill"):
+        return bench_prefill(args, window_left)
+
+    if args.workload == "small":
+        kv_lens = decode_lengths(32, 2048, 8192, 1002)
+    else:
+        kv_lens = decode_lengths(64, 4096, 32768, 1002)
+    table, n_pages = make_tables(kv_lens, 1002)
+    batch = len(kv_lens)
+    workload_name = {
+        "decode_global": "config 2: decode attention, batch 64, ctx log-uniform [4096, 32768], "
+                         "global layer",
+        "decode_local": "config 2: decode attention, batch 64, ctx log-uniform [4096, 32768], "
+                        "local layer (window 8192)",
+        "small": "profiling case: decode attention, batch 32, ctx log-uniform [2048, 8192]",
+    }[args.workload]
+
+    # ------------------------------------------------------------ reference arm
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        g = torch.Generator().manual_seed(1002)
+
+        def rows_fn(pages):
+            return torch.randn(len(pages) * PAGE, HKV * 2 * D, generator=g).to(torch.bfloat16)
+
+        times, vals = [], []
+        per_step = max(2.0, min(args.cpu_seconds, 120.0 / max(1, args.steps + args.warmup)))
+        res = None
+        for i in range(args.warmup + args.steps):
+            res = cpu_decode_baseline(kv_lens, table, rows_fn, window_left, HQ, HKV, per_step, i)
+            if i >= args.warmup:
+                vals.append(res["value"])
+        value = statistics.mean(vals)
+        res["value"] = value
+        total_bytes = decode_bytes(kv_lens, window_left, HQ, HKV)
+        print(json.dumps({
+            "impl": "reference", "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s",
+            "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": total_bytes / (value * 1e9) * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": workload_name, "batch": batch, "heads": f"{HQ}q/{HKV}kv",
+                       "head_dim": D, "page_size": PAGE, "window_left": window_left,
+                       "note": "CPU restatement of the reference path on the host cores; each "
+                               "step times a bounded sample and ms_per_step is scaled to the "
+                               "whole batch"},
+            "cpu_baseline": res,
+            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0},
+        }))
+        return
+
+    # ---------------------------------------------------------------- B200 arm
+    import cwm_b200
+    from cwm_b200 import _lib
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback)")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    hkv_l, hq_l = HKV // n_gpus, HQ // n_gpus
+
+    gen = torch.Generator(device=dev).manual_seed(1002 + rank)
+    cache = cwm_b200.RawCache.build_dims(1, hkv_l, D, n_pages * PAGE, dev, torch.bfloat16)
+    row = cache.caches[0]
+    chunk = 1 << 16
+    for r0 in range(0, row.shape[0], chunk):
+        blk = row[r0 : r0 + chunk]
+        blk.copy_(torch.randn(blk.shape, generator=gen, device=dev, dtype=torch.float32))
+    table_d = table.to(dev)
+    # metadata of a decode step *before* the new token is appended
+    lens_before = [n - 1 for n in kv_lens]
+    bias = cwm_b200.AttnBias.from_seqlens([1] * batch, kv_lens, table_d, PAGE)
+    freqs = cwm_b200.rope_freqs(D, 1e6).to(dev)
+    q_pos = torch.tensor(lens_before, dtype=torch.int32, device=dev)
+    xq = torch.randn(batch, hq_l, D, generator=gen, device=dev).to(torch.bfloat16)
+    xk = torch.randn(batch, hkv_l, D, generator=gen, device=dev).to(torch.bfloat16)
+    xv = torch.randn(batch, hkv_l, D, generator=gen, device=dev).to(torch.bfloat16)
+    cache_k, cache_v = cache.cache_kv(0)
+    k4 = cache_k.reshape(-1, PAGE, hkv_l, D)
+    v4 = cache_v.reshape(-1, PAGE, hkv_l, D)
+    # write the step's own token so that the cache is complete
+    cwm_b200.rope_kv_write(xq, xk, xv, cache_k, cache_v, q_pos, freqs, table_d, None, None, PAGE)
+
+    def attn_step():
+        return cwm_b200.mha_fwd(
+            xq, k4, v4, bias.q_seqinfo.seqstart, None, bias.k_seqinfo.seqlen, None, 1,
+            bias.k_seqinfo.max_seqlen, 0, table_d, D**-0.5, True, window_left, -1,
+        )
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        attn_step()
+    sync_all()
+    start = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stop = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    with ClockSampler(local_rank) as clocks:
+        sync_all()
+        for i in range(args.steps):
+            start[i].record()
+            attn_step()
+            stop[i].record()
+        sync_all()
+        # keep the sampler alive for at least a few samples on very short runs
+        if sum(s.elapsed_time(e) for s, e in zip(start, stop)) < 500:
+            t_end = time.time() + 0.6
+            while time.time() < t_end:
+                attn_step()
+            torch.cuda.synchronize()
+    step_ms = [s.elapsed_time(e) for s, e in zip(start, stop)]
+    total_ms = torch.tensor([sum(step_ms)], device=dev)
+    if dist is not None:
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    total_ms = float(total_ms.item())
+    ms_per_step = total_ms / args.steps
+    status = _lib.device_status(torch.cuda.current_stream().cuda_stream)
+    if status != 0:
+        raise SystemExit(f"device status word is {status} after the timed region")
+
+    bytes_rank = decode_bytes(kv_lens, window_left, hq_l, hkv_l)
+    bytes_all = bytes_rank * n_gpus
+    value = bytes_all / (ms_per_step * 1e-3) / 1e9
+    peaks, peak_kind = measured_peaks()
+    achieved = bytes_rank / (statistics.mean(step_ms) * 1e-3) / 1e9
+
+    # -------------------------------------------------- end to end, host buffers
+    h_q = torch.randn(batch, hq_l, D).to(torch.bfloat16).pin_memory()
+    h_k = torch.randn(batch, hkv_l, D).to(torch.bfloat16).pin_memory()
+    h_v = torch.randn(batch, hkv_l, D).to(torch.bfloat16).pin_memory()
+    h_out = torch.empty(batch, hq_l, D, dtype=torch.bfloat16).pin_memory()
+    d_q, d_k, d_v = torch.empty_like(xq), torch.empty_like(xk), torch.empty_like(xv)
+
+    def e2e_step():
+        d_q.copy_(h_q, non_blocking=True)
+        d_k.copy_(h_k, non_blocking=True)
+        d_v.copy_(h_v, non_blocking=True)
+        out = cwm_b200.gqa_attention(d_q, d_k, d_v, cache, 0, bias, q_pos, None, None, freqs,
+                                     window_left)
+        h_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    sync_all()
+    e2e_ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if dist is not None:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_value = bytes_all / (float(e2e_ms.item()) / args.steps * 1e-3) / 1e9
+    h2d = (h_q.numel() + h_k.numel() + h_v.numel()) * 2
+    d2h = h_out.numel() * 2
+
+    line = {
+        "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": n_gpus,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": workload_name, "batch": batch, "heads": f"{HQ}q/{HKV}kv",
+                   "heads_per_gpu": f"{hq_l}q/{hkv_l}kv", "head_dim": D, "page_size": PAGE,
+                   "window_left": window_left, "kv_bytes_per_gpu": bytes_rank,
+                   "l2": "inputs larger than L2" if bytes_rank > 2 * L2_BYTES else
+                         "inputs not larger than L2 at this sharding", "parallelism": f"tp{n_gpus}"},
+        "clocks": clocks.summary(),
+        "gpu_launches": 2 * args.steps,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h,
+                "note": "per step: H2D of the step's q/k/v rows from pinned memory, fused rotary "
+                        "+ KV-cache write, attention, D2H of the output; the KV cache is "
+                        "device-resident state as in the reference engine"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                     "peak_kind": f"of {peak_kind}",
+                     "note": "per GPU; events bracket the decode kernel and its combine kernel"},
+    }
+    if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
+        def rows_fn(pages):
+            return torch.cat([row[int(pg) * PAGE : (int(pg) + 1) * PAGE] for pg in pages]).cpu()
+
+        line["cpu_baseline"] = cpu_decode_baseline(
+            kv_lens, table, rows_fn, window_left, HQ, HKV, args.cpu_seconds, 7
+        )
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def bench_prefill(args, window_left: int) -> None:
+    """Chunked prefill (config 3 shapes): 8 sequences, one 2048-token chunk each per
+    step, cached prefixes uniform in [0, 16384] plus the chunk index."""
+    import cwm_b200
+    from cwm_b200.layer import prefill_positions
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(1003)
+    n0s = torch.randint(0, 16385, (8,), generator=g).tolist()
+    peaks, peak_kind = measured_peaks()
+    results = []
+    for chunk in range(4):
+        seq_info = [(n0 + 2048 * chunk, 2048) for n0 in n0s]
+        kv_lens = [a + b for a, b in seq_info]
+        table, n_pages = make_tables(kv_lens, 1003)
+        cache = cwm_b200.RawCache.build_dims(1, HKV, D, n_pages * PAGE, dev, torch.bfloat16)
+        cache.caches[0].normal_()
+        bias = cwm_b200.AttnBias.from_seqlens([2048] * 8, kv_lens, table.to(dev), PAGE)
+        q_batch, q_pos = prefill_positions(seq_info, dev)
+        freqs = cwm_b200.rope_freqs(D, 1e6).to(dev)
+        t = 8 * 2048
+        xq = torch.randn(t, HQ, D, device=dev).to(torch.bfloat16)
+        xk = torch.randn(t, HKV, D, device=dev).to(torch.bfloat16)
+        xv = torch.randn(t, HKV, D, device=dev).to(torch.bfloat16)
+
+        def step():
+            return cwm_b200.gqa_attention(xq, xk, xv, cache, 0, bias, q_pos, q_batch, None, freqs,
+                                          window_left)
+
+        for _ in range(max(3, args.warmup)):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        flops = 4 * D * HQ * prefill_pairs(seq_info, window_left)
+        results.append((ms, flops))
+        del cache
+    total_ms = sum(r[0] for r in results)
+    total_flops = sum(r[1] for r in results)
+    tf = total_flops / (total_ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "prefill_attn_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": total_ms,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "config 3: chunked prefill 8 x 8192 tokens in 2048-token chunks, "
+                               "fused rotary + KV write + attention", "window_left": window_left,
+                   "per_chunk_ms": [r[0] for r in results]},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"],
+                     "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"], "traffic": None,
+                     "peak_kind": f"of {peak_kind}"},
+    }))
+
+
+if __name__ == "__main__":
+    main()

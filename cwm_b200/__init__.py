@@ -1,0 +1,36 @@
+"""B200 (sm_100a) kernels for the attention hot path of CWM's FastGen engine.
+
+The public names mirror the reference's call sites so that they drop in:
+
+* ``apply_rope``, ``paged_memcpy``, ``rmsnorm`` — ``cwm/fastgen/kernels``;
+* ``mha_fwd`` — ``xformers.ops.fmha.flash3.mha_fwd`` as called by
+  ``cwm/fastgen/forward.py:639-655``;
+* ``AttnBias`` — the paged block-diagonal causal mask metadata of
+  ``forward.py:12-14``;
+* ``RawCache`` / ``ModelCache`` — ``cwm/fastgen/utils/cache.py``;
+* ``gqa_attention`` — the GQA branch of ``forward.py:608-656`` in two launches.
+
+Everything runs through ``libcwm_b200.so``; there is no CPU or Triton fallback.
+"""
+
+from .attention import mha_fwd, rope_kv_write, workspace_for
+from .attn_bias import AttnBias, PagedBlockDiagonalCausalWithOffsetPaddedKeysMask
+from .cache import ModelCache, RawCache
+from .kernels import apply_rope, paged_memcpy, rmsnorm
+from .layer import gqa_attention, rope_freqs, window_size_left
+
+__all__ = [
+    "AttnBias",
+    "ModelCache",
+    "PagedBlockDiagonalCausalWithOffsetPaddedKeysMask",
+    "RawCache",
+    "apply_rope",
+    "gqa_attention",
+    "mha_fwd",
+    "paged_memcpy",
+    "rmsnorm",
+    "rope_freqs",
+    "rope_kv_write",
+    "window_size_left",
+    "workspace_for",
+]

@@ -1,0 +1,271 @@
+"""Paged-KV grouped-query attention and the fused rotate + cache-write step.
+
+``mha_fwd`` keeps the signature with which ``cwm/fastgen/forward.py:639-655``
+calls ``xformers.ops.fmha.flash3.mha_fwd``; ``rope_kv_write`` does in one launch
+what ``forward.py:618-632`` does in four (two ``apply_rope`` and two
+``paged_memcpy`` calls).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .kernels import _DTYPES, _ptr, _require_cuda, _stream
+
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+# batch size the cached workspace is sized for; larger batches get a fresh one
+_WS_BATCH = 16384
+
+
+def workspace_for(device: torch.device, batch: int) -> torch.Tensor:
+    """Scratch buffer for ``mha_fwd`` on ``device`` (split-KV partial results and
+    the tile prefix of the decode scheduler).
+
+    One buffer per device and stream is cached and shared by all calls on that
+    stream, which is safe because calls on one stream run in order.  While a CUDA
+    graph is being captured a fresh buffer is taken from the graph's pool instead,
+    so that the captured kernels never point at memory the cache could drop.
+    """
+    lib = _lib.load()
+    if torch.cuda.is_current_stream_capturing():
+        need = lib.cwm_paged_attn_workspace_bytes(batch, 0, 0, 0, 0)
+        return torch.empty(need, dtype=torch.uint8, device=device)
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    need = lib.cwm_paged_attn_workspace_bytes(max(batch, _WS_BATCH), 0, 0, 0, 0)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(need, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+@torch.library.custom_op("cwm_b200::paged_attn_fwd", mutates_args=(), device_types="cuda")
+def _paged_attn_op(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    seqused_k: torch.Tensor,
+    block_table: torch.Tensor,
+    max_seqlen_q: int,
+    max_seqlen_k: int,
+    softmax_scale: float,
+    window_left: int,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    total_q, hq, d = query.shape
+    num_pages, page_size, hkv, _ = key.shape
+    batch = seqused_k.shape[0]
+    out = torch.empty_like(query)
+    lse = torch.empty((hq, total_q), dtype=torch.float32, device=query.device)
+    if total_q == 0 or batch == 0:
+        return out, lse
+    ws = workspace_for(query.device, batch)
+    with torch.cuda.device(query.device):
+        code = _lib.load().cwm_paged_attn_fwd(
+            query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(), lse.data_ptr(),
+            cu_seqlens_q.data_ptr(), seqused_k.data_ptr(), block_table.data_ptr(), batch,
+            total_q, hq, hkv, d, _DTYPES[query.dtype], page_size, num_pages, key.stride(1),
+            block_table.stride(0), max_seqlen_q, max_seqlen_k, softmax_scale, window_left,
+            ws.data_ptr(), ws.numel(), _stream(query),
+        )
+    _lib.check(code, "mha_fwd")
+    return out, lse
+
+
+@_paged_attn_op.register_fake
+def _(query, key, value, cu_seqlens_q, seqused_k, block_table, max_seqlen_q, max_seqlen_k,
+      softmax_scale, window_left):
+    return torch.empty_like(query), query.new_empty(
+        (query.shape[1], query.shape[0]), dtype=torch.float32
+    )
+
+
+def mha_fwd(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    cu_seqlens_k: torch.Tensor | None,
+    seqused_k: torch.Tensor,
+    leftpad_k: torch.Tensor | None,
+    max_seqlen_q: int,
+    max_seqlen_k: int,
+    p: float,
+    block_table: torch.Tensor,
+    softmax_scale: float,
+    is_causal: bool = True,
+    window_left: int = -1,
+    window_right: int = -1,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Variable-length paged grouped-query attention forward.
+
+    Same arguments as the call at ``cwm/fastgen/forward.py:639-655``:
+
+    * ``query``: ``(T, Hq, 128)`` contiguous, bf16 or fp16;
+    * ``key``, ``value``: ``(pages, page_size, Hkv, 128)`` views of the cache rows
+      (``cache_k.reshape(-1, page_size, Hkv, 128)``): unit stride in the last
+      dimension, heads contiguous, any token stride;
+    * ``cu_seqlens_q``: int32 ``(B + 1,)`` query offsets; ``seqused_k``: int32
+      ``(B,)`` keys per sequence (including the queries' own tokens);
+    * ``block_table``: int32 ``(B, cols)``, row stride free;
+    * ``max_seqlen_q`` / ``max_seqlen_k``: static upper bounds (in graph-captured
+      decode ``max_seqlen_k`` is the cache capacity of a lane, not the true
+      maximum);
+    * ``window_left``: keys further than this to the left of the query are
+      masked; negative means unbounded.
+
+    Only what the reference uses is built: ``cu_seqlens_k`` and ``leftpad_k`` must
+    be None, ``p`` 0, ``is_causal`` True and ``window_right`` -1 or 0.
+
+    Returns ``(out, lse)`` with ``out`` like ``query`` and ``lse`` float32
+    ``(Hq, T)``.
+    """
+    if cu_seqlens_k is not None or leftpad_k is not None:
+        raise ValueError("cu_seqlens_k and leftpad_k are not supported (pass None)")
+    if p != 0:
+        raise ValueError("dropout is not supported (p must be 0)")
+    if not is_causal or window_right not in (-1, 0):
+        raise ValueError("only causal attention (is_causal=True, window_right=-1) is supported")
+    if query.ndim != 3:
+        raise ValueError(f"query must be (T, Hq, D), got {query.ndim}-D")
+    if key.ndim != 4 or value.ndim != 4 or key.shape != value.shape:
+        raise ValueError("key and value must be (pages, page_size, Hkv, D) with equal shapes")
+    if query.dtype not in (torch.bfloat16, torch.float16):
+        raise ValueError(f"query must be bf16 or fp16, got {query.dtype}")
+    if key.dtype != query.dtype or value.dtype != query.dtype:
+        raise ValueError("query, key and value must share a dtype")
+    if not query.is_contiguous():
+        raise ValueError("query must be contiguous")
+    _, hq, d = query.shape
+    _, page_size, hkv, dk = key.shape
+    if dk != d:
+        raise ValueError(f"head dimensions differ: query {d}, key {dk}")
+    if hkv == 0 or hq % hkv != 0:
+        raise ValueError(f"{hq} query heads cannot be grouped over {hkv} KV heads")
+    for name, t in (("key", key), ("value", value)):
+        if t.stride(3) != 1 or (hkv > 1 and t.stride(2) != d):
+            raise ValueError(f"{name} must keep heads contiguous within a token row")
+        if t.shape[0] > 1 and t.stride(0) != page_size * t.stride(1):
+            raise ValueError(f"{name} pages must be consecutive row ranges of the cache")
+    if key.stride(1) != value.stride(1):
+        raise ValueError("key and value must have the same token stride")
+    for name, t in (("cu_seqlens_q", cu_seqlens_q), ("seqused_k", seqused_k)):
+        if t.dtype != torch.int32 or t.ndim != 1 or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous 1-D int32 tensor")
+    batch = seqused_k.shape[0]
+    if cu_seqlens_q.shape[0] != batch + 1:
+        raise ValueError(f"cu_seqlens_q must have {batch + 1} entries, got {cu_seqlens_q.shape[0]}")
+    if block_table.dtype != torch.int32 or block_table.ndim != 2:
+        raise ValueError("block_table must be a 2-D int32 tensor")
+    if block_table.shape[0] < batch:
+        raise ValueError("block_table has fewer rows than sequences")
+    if block_table.shape[1] > 1 and block_table.stride(1) != 1:
+        raise ValueError("block_table must have unit stride in its last dimension")
+    _require_cuda("mha_fwd", query, key, value, cu_seqlens_q, seqused_k, block_table)
+    # never read past the block table, whatever bound the caller gave
+    max_k = min(int(max_seqlen_k), block_table.shape[1] * page_size)
+    return _paged_attn_op(
+        query, key, value, cu_seqlens_q, seqused_k, block_table, int(max_seqlen_q), max_k,
+        float(softmax_scale), int(window_left),
+    )
+
+
+@torch.library.custom_op(
+    "cwm_b200::rope_kv_write", mutates_args=("xq", "xk", "cache_k", "cache_v"),
+    device_types="cuda",
+)
+def _rope_kv_write_op(
+    xq: torch.Tensor,
+    xk: torch.Tensor,
+    xv: torch.Tensor,
+    cache_k: torch.Tensor,
+    cache_v: torch.Tensor,
+    pos: torch.Tensor,
+    freqs: torch.Tensor,
+    page_tbl: torch.Tensor,
+    src_batch: torch.Tensor | None,
+    batch_size: torch.Tensor | None,
+    page_size: int,
+) -> None:
+    t, hq, d = xq.shape
+    hkv = xk.shape[1]
+    with torch.cuda.device(xq.device):
+        code = _lib.load().cwm_rope_kv_write(
+            xq.data_ptr(), xk.data_ptr(), xv.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(),
+            pos.data_ptr(), freqs.data_ptr(), page_tbl.data_ptr(), _ptr(src_batch),
+            _ptr(batch_size), int(batch_size is not None and batch_size.dtype == torch.int64),
+            t, hq, hkv, d, _DTYPES[xq.dtype], page_size, page_tbl.stride(0), page_tbl.shape[1],
+            cache_k.stride(0), cache_k.shape[0], _stream(xq),
+        )
+    _lib.check(code, "rope_kv_write")
+
+
+def rope_kv_write(
+    xq: torch.Tensor,
+    xk: torch.Tensor,
+    xv: torch.Tensor,
+    cache_k: torch.Tensor,
+    cache_v: torch.Tensor,
+    pos: torch.Tensor,
+    freqs: torch.Tensor,
+    page_tbl: torch.Tensor,
+    src_batch: torch.Tensor | None,
+    batch_size: torch.Tensor | None,
+    page_size: int,
+) -> None:
+    """Rotate ``xq`` and ``xk`` in place and store the rotated ``xk`` and ``xv``
+    rows in their pages, in one launch.
+
+    Equivalent to the sequence at ``cwm/fastgen/forward.py:618-632``::
+
+        apply_rope(xq, pos, freqs); apply_rope(xk, pos, freqs)
+        paged_memcpy(xk.flatten(1, 2), cache_k, page_tbl, pos, None, src_batch, batch_size, P)
+        paged_memcpy(xv.flatten(1, 2), cache_v, page_tbl, pos, None, src_batch, batch_size, P)
+
+    ``xq``: ``(T, Hq, D)``; ``xk``, ``xv``: ``(T, Hkv, D)``; ``cache_k``/``cache_v``:
+    the two column halves of a cache layer as returned by ``RawCache.cache_kv``.
+    Rows at or beyond ``batch_size`` are rotated but not stored, as in the
+    reference.
+    """
+    if xq.ndim != 3 or xk.ndim != 3 or xv.ndim != 3:
+        raise ValueError("xq, xk and xv must be 3-D (T, H, D)")
+    t, _, d = xq.shape
+    if xk.shape[0] != t or xv.shape != xk.shape or xk.shape[2] != d:
+        raise ValueError("xq, xk and xv disagree on the token count or head dimension")
+    if not (xq.is_contiguous() and xk.is_contiguous() and xv.is_contiguous()):
+        raise ValueError("xq, xk and xv must be contiguous")
+    if not (xq.dtype == xk.dtype == xv.dtype == cache_k.dtype == cache_v.dtype):
+        raise ValueError("xq, xk, xv and the cache must share a dtype")
+    if xq.dtype not in _DTYPES:
+        raise ValueError(f"dtype {xq.dtype} is not supported")
+    hkv = xk.shape[1]
+    for name, c in (("cache_k", cache_k), ("cache_v", cache_v)):
+        if c.ndim != 2 or c.shape[1] != hkv * d or c.stride(1) != 1:
+            raise ValueError(f"{name} must be (rows, Hkv * D) with unit stride in its last dimension")
+    if cache_k.stride(0) != cache_v.stride(0) or cache_k.shape[0] != cache_v.shape[0]:
+        raise ValueError("cache_k and cache_v must be halves of the same cache rows")
+    if pos.dtype != torch.int32 or pos.ndim != 1 or pos.shape[0] != t or not pos.is_contiguous():
+        raise ValueError(f"pos must be a contiguous int32 tensor of shape ({t},)")
+    if freqs.dtype != torch.float32 or freqs.ndim != 1 or freqs.shape[0] * 2 != d:
+        raise ValueError(f"freqs must be a float32 tensor of shape ({d // 2},)")
+    if not freqs.is_contiguous():
+        raise ValueError("freqs must be contiguous")
+    if page_tbl.dtype != torch.int32 or page_tbl.ndim != 2:
+        raise ValueError("page_tbl must be a 2-D int32 tensor")
+    if page_tbl.shape[1] > 1 and page_tbl.stride(1) != 1:
+        raise ValueError("page_tbl must have unit stride in its last dimension")
+    if src_batch is not None:
+        if (src_batch.dtype != torch.int32 or src_batch.ndim != 1 or src_batch.shape[0] != t
+                or not src_batch.is_contiguous()):
+            raise ValueError(f"src_batch must be a contiguous int32 tensor of shape ({t},)")
+    if batch_size is not None:
+        if batch_size.ndim != 0 or batch_size.dtype not in (torch.int32, torch.int64):
+            raise ValueError("batch_size must be a 0-d int32 or int64 tensor")
+        if src_batch is not None:
+            raise ValueError("src_batch and batch_size cannot be given together")
+    _require_cuda("rope_kv_write", xq, xk, xv, cache_k, cache_v, pos, freqs, page_tbl,
+                  src_batch, batch_size)
+    _rope_kv_write_op(xq, xk, xv, cache_k, cache_v, pos, freqs, page_tbl, src_batch, batch_size,
+                      page_size)

@@ -1,0 +1,68 @@
+// Argument blocks and launch entry points shared by the attention kernels.
+#pragma once
+
+#include <math.h>
+
+#include "common.cuh"
+
+namespace cwm {
+
+constexpr int kHeadDim = 128;
+// Upper bound on the persistent decode grid; sizes the split-KV workspace.
+constexpr int kMaxDecodeCtas = 1024;
+
+// Everything the attention kernels read besides the K/V tensor maps.
+struct AttnArgs {
+  const void* q;               // [total_q, hq, 128]
+  void* out;                   // [total_q, hq, 128]
+  float* lse;                  // [hq, total_q] or null
+  const int32_t* cu_q;         // [batch + 1]
+  const int32_t* seq_k;        // [batch]
+  const int32_t* block_table;  // [batch, *], row stride bt_stride
+  int batch;
+  int hq;
+  int hkv;
+  int group;  // hq / hkv
+  int page_size;
+  int max_seqlen_q;
+  int max_seqlen_k;
+  long long num_pages;
+  long long bt_stride;
+  long long total_q;
+  float scale_log2;  // softmax_scale * log2(e)
+  int window_left;   // < 0: unbounded
+  int* prefix;       // workspace: int[batch + 1], tile prefix written by the decode kernel
+  float* partial;    // workspace: split-KV partial states
+  int* status;       // device status word
+};
+using DecodeArgs = AttnArgs;
+
+size_t decode_workspace_bytes(int batch);
+int launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, AttnArgs a, bool bf16,
+                  void* workspace, cudaStream_t stream);
+int launch_prefill(const CUtensorMap& kmap, const CUtensorMap& vmap, AttnArgs a, bool bf16,
+                   cudaStream_t stream);
+
+// mma.sync m16n8k16 where only rows 0..7 of the accumulator are kept: the two
+// values of rows 8..15 go to scratch registers and enter as zero, so that
+// independent products do not chain through them.
+template <bool kBf16>
+__device__ __forceinline__ void mma_16816_top(float (&c)[2], const uint32_t (&a)[4], uint32_t b0,
+                                              uint32_t b1) {
+  float j0, j1;
+  if constexpr (kBf16) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%10,%10};"
+        : "+f"(c[0]), "+f"(c[1]), "=f"(j0), "=f"(j1)
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%10,%10};"
+        : "+f"(c[0]), "+f"(c[1]), "=f"(j0), "=f"(j1)
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+  }
+}
+
+}  // namespace cwm

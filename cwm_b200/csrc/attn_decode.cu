@@ -1,0 +1,487 @@
+// Split-KV paged GQA decode attention for sm_100a (one query token per sequence).
+//
+// The kernel is HBM-bound: every K/V byte of the attended window is read once and
+// serves all query heads of its GQA group.  Work is cut into tiles of 64 tokens
+// of one (sequence, KV head); the flat list of tiles is divided evenly over a
+// fixed, persistent grid (2 CTAs per SM), so the launch shape does not depend on
+// the sequence lengths, which are read on the device (CUDA-graph friendly).
+//
+// Per CTA: one producer warp streams tiles into a 3-stage shared-memory ring with
+// TMA tile loads (128-byte swizzle) through the block table; four consumer warps
+// each take 16 tokens of a tile, compute S = Q K^T and O += P V with
+// mma.sync.m16n8k16 (query heads on the M rows, fp32 online softmax with
+// warp-shuffle row reductions), and keep their own running (max, sum, O).  When a
+// (sequence, KV head) segment ends, the four warp states are merged through
+// shared memory; a segment that lies wholly inside one CTA is written straight to
+// the output, otherwise the CTA leaves a partial (max, sum, O) in the workspace
+// and the combine kernel merges the partials of that segment in a fixed order.
+#include "attn_common.cuh"
+
+namespace cwm {
+namespace {
+
+constexpr int kTile = 64;
+constexpr int kStages = 3;
+constexpr int kConsumerWarps = 4;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kBoxBytes = kTile * 128;       // one [64 rows x 128 B] TMA box
+constexpr int kStageBytes = 4 * kBoxBytes;   // K lo, K hi, V lo, V hi
+constexpr int kFragFloats = 34;              // 16 x 2 output values, max, sum
+constexpr int kPartialFloats = kFragFloats * 32;
+
+struct SeqInfo {
+  int ctx;     // keys of the sequence
+  int lo;      // first attended key
+  int tile0;   // first attended tile (absolute tile index)
+  int ntiles;  // attended tiles (0: not a decode sequence, or empty)
+  int qtok;    // row of the query in q / out
+};
+
+__device__ __forceinline__ SeqInfo seq_info(const DecodeArgs& a, int b) {
+  SeqInfo s;
+  const int q0 = a.cu_q[b];
+  const int q1 = a.cu_q[b + 1];
+  int ctx = a.seq_k[b];
+  ctx = ctx > a.max_seqlen_k ? a.max_seqlen_k : ctx;
+  s.qtok = q0;
+  s.ctx = ctx;
+  if (q1 - q0 != 1 || ctx <= 0) {
+    s.lo = 0;
+    s.tile0 = 0;
+    s.ntiles = 0;
+    return s;
+  }
+  s.lo = a.window_left >= 0 ? max(0, ctx - 1 - a.window_left) : 0;
+  s.tile0 = s.lo / kTile;
+  s.ntiles = (ctx - 1) / kTile - s.tile0 + 1;
+  return s;
+}
+
+// Largest b with prefix[b] <= g (prefix is non-decreasing, prefix[batch] > g).
+__device__ __forceinline__ int find_seq(const int* prefix, int batch, int g) {
+  int lo = 0, hi = batch;  // answer in [lo, hi)
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (prefix[mid] <= g) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// Per-thread slice of a warp's running state, in mma C-fragment layout: the
+// thread with lane = 4 * head + c holds output columns 8 j + 2 c + {0, 1}.
+struct Frag {
+  float o[16][2];
+  float m;  // running max (scaled, log2 domain); equal across the 4 lanes of a head
+  float l;  // running sum (per-thread partial until quad_reduce_l)
+};
+
+__device__ __forceinline__ void frag_reset(Frag& f) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) f.o[j][0] = f.o[j][1] = 0.f;
+  f.m = -INFINITY;
+  f.l = 0.f;
+}
+
+__device__ __forceinline__ void frag_store(const Frag& f, float* buf, int lane) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    buf[(2 * j) * 32 + lane] = f.o[j][0];
+    buf[(2 * j + 1) * 32 + lane] = f.o[j][1];
+  }
+  buf[32 * 32 + lane] = f.m;
+  buf[33 * 32 + lane] = f.l;
+}
+
+// f <- merge(f, state stored at buf); both with fully reduced sums.
+__device__ __forceinline__ void frag_merge(Frag& f, const float* buf, int lane) {
+  const float mb = buf[32 * 32 + lane];
+  const float lb = buf[33 * 32 + lane];
+  const float mn = fmaxf(f.m, mb);
+  const float mu = mn == -INFINITY ? 0.f : mn;
+  const float sa = fast_exp2(f.m - mu);
+  const float sb = fast_exp2(mb - mu);
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    f.o[j][0] = f.o[j][0] * sa + buf[(2 * j) * 32 + lane] * sb;
+    f.o[j][1] = f.o[j][1] * sa + buf[(2 * j + 1) * 32 + lane] * sb;
+  }
+  f.l = f.l * sa + lb * sb;
+  f.m = mn;
+}
+
+// Normalise and store one finished (sequence, KV head) result.
+template <bool kBf16>
+__device__ __forceinline__ void frag_write_out(const Frag& f, const DecodeArgs& a, int qtok,
+                                               int kv_head, int lane) {
+  const int g = lane >> 2;
+  if (g >= a.group) return;
+  const int c = lane & 3;
+  const int head = kv_head * a.group + g;
+  const float inv = f.l > 0.f ? 1.f / f.l : 0.f;
+  uint32_t* orow = reinterpret_cast<uint32_t*>(a.out) +
+                   (static_cast<long long>(qtok) * a.hq + head) * (kHeadDim / 2);
+#pragma unroll
+  for (int j = 0; j < 16; ++j) orow[j * 4 + c] = pack2<kBf16>(f.o[j][0] * inv, f.o[j][1] * inv);
+  if (a.lse != nullptr && c == 0) {
+    a.lse[static_cast<long long>(head) * a.total_q + qtok] =
+        f.l > 0.f ? (f.m + log2f(f.l)) * 0.6931471805599453f : -INFINITY;
+  }
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kThreads, 2)
+decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+              const DecodeArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // layout: stages | merge buffers (2 partials) | barriers | prefix
+  uint8_t* stages = smem_raw;
+  float* merge_buf = reinterpret_cast<float*>(smem_raw + kStages * kStageBytes);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(merge_buf + 2 * kPartialFloats);
+  uint64_t* empty_bar = full_bar + kStages;
+  int* prefix = reinterpret_cast<int*>(empty_bar + kStages);
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kConsumerWarps);
+    }
+    fence_mbar_init();
+    prefetch_tensormap(&kmap);
+    prefetch_tensormap(&vmap);
+  }
+  // tiles per sequence -> exclusive prefix over sequences (times KV heads)
+  for (int b = tid; b < a.batch; b += kThreads) prefix[b + 1] = seq_info(a, b).ntiles * a.hkv;
+  if (tid == 0) prefix[0] = 0;
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    for (int base = 0; base < a.batch; base += 32) {
+      const int idx = base + lane;
+      int v = idx < a.batch ? prefix[idx + 1] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += t;
+      }
+      if (idx < a.batch) prefix[idx + 1] = v + carry;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  __syncthreads();
+  const int total = prefix[a.batch];
+  if (blockIdx.x == 0) {
+    for (int b = tid; b <= a.batch; b += kThreads) a.prefix[b] = prefix[b];
+  }
+  const int per = (total + gridDim.x - 1) / gridDim.x;
+  const int g_begin = min(total, static_cast<int>(blockIdx.x) * per);
+  const int g_end = min(total, g_begin + per);
+  if (g_begin >= g_end) return;
+
+  if (warp == kConsumerWarps) {
+    // ------------------------------------------------------------ producer warp
+    int issued = 0;
+    bool ok = true;
+    for (int g0 = g_begin; g0 < g_end && ok; g0 += 32) {
+      const int g = g0 + lane;
+      int x = 0, row = 0;
+      if (g < g_end) {
+        const int b = find_seq(prefix, a.batch, g);
+        const int r = g - prefix[b];
+        const int nt = (prefix[b + 1] - prefix[b]) / a.hkv;
+        const int h = r / nt;
+        const int t = r - h * nt;
+        const SeqInfo si = seq_info(a, b);
+        const int tok = (si.tile0 + t) * kTile;
+        long long page = a.block_table[static_cast<long long>(b) * a.bt_stride + tok / a.page_size];
+        if (page < 0 || page >= a.num_pages) {
+          atomicOr(a.status, DEV_BAD_PAGE);
+          page = 0;
+        }
+        row = static_cast<int>(page * a.page_size + tok % a.page_size);
+        x = h * kHeadDim;
+      }
+      const int cnt = min(32, g_end - g0);
+      for (int j = 0; j < cnt; ++j) {
+        const int xj = __shfl_sync(0xffffffffu, x, j);
+        const int rj = __shfl_sync(0xffffffffu, row, j);
+        if (lane == 0) {
+          const int s = issued % kStages;
+          const uint32_t ph = (issued / kStages) & 1;
+          if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1)) {
+            ok = false;
+          } else {
+            uint8_t* st = stages + s * kStageBytes;
+            mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
+            tma_load_2d(st, &kmap, xj, rj, &full_bar[s]);
+            tma_load_2d(st + kBoxBytes, &kmap, xj + 64, rj, &full_bar[s]);
+            tma_load_2d(st + 2 * kBoxBytes, &vmap, xj, rj, &full_bar[s]);
+            tma_load_2d(st + 3 * kBoxBytes, &vmap, xj + 64, rj, &full_bar[s]);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        ++issued;
+      }
+    }
+    if (!ok && lane == 0) {
+      atomicOr(a.status, DEV_WAIT_TIMEOUT);
+      atomicExch(&abort_flag, 1);
+    }
+    // Do not leave while copies are in flight: wait (bounded) for the stages
+    // that were issued but possibly not consumed yet.
+    if (lane == 0) {
+      const int first = issued > kStages ? issued - kStages : 0;
+      for (int i = first; i < issued; ++i) {
+        const int s = i % kStages;
+        const uint32_t ph = (i / kStages) & 1;
+        if (!mbar_wait_bounded(&full_bar[s], ph)) {
+          atomicOr(a.status, DEV_WAIT_TIMEOUT);
+          break;
+        }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------- consumer warps
+  const int g = lane >> 2;  // query head within the group (rows 6, 7 are padding for CWM)
+  const int c = lane & 3;
+  int b = find_seq(prefix, a.batch, g_begin);
+  SeqInfo si = seq_info(a, b);
+  int rel = g_begin - prefix[b];
+  int h = rel / si.ntiles;
+  int t = rel - h * si.ntiles;
+  int seg_start = g_begin - t;  // global tile index at which this segment starts
+
+  Frag f;
+  frag_reset(f);
+  uint32_t qa[8][2];
+  auto load_q = [&]() {
+    const uint32_t* qrow = reinterpret_cast<const uint32_t*>(a.q) +
+                           (static_cast<long long>(si.qtok) * a.hq + h * a.group + g) *
+                               (kHeadDim / 2);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      qa[ks][0] = g < a.group ? qrow[ks * 8 + c] : 0u;
+      qa[ks][1] = g < a.group ? qrow[ks * 8 + 4 + c] : 0u;
+    }
+  };
+  load_q();
+
+  // Merge the four warp states and write the segment's result or partial.
+  auto flush = [&](int seg_end) {
+    // reduce the per-thread partial sums over the 4 lanes of a head
+    f.l += __shfl_xor_sync(0xffffffffu, f.l, 1);
+    f.l += __shfl_xor_sync(0xffffffffu, f.l, 2);
+    named_bar_sync(1, kConsumerWarps * 32);  // merge buffers free (previous flush done)
+    if (warp >= 2) frag_store(f, merge_buf + (warp - 2) * kPartialFloats, lane);
+    named_bar_sync(1, kConsumerWarps * 32);
+    if (warp < 2) frag_merge(f, merge_buf + warp * kPartialFloats, lane);
+    named_bar_sync(1, kConsumerWarps * 32);
+    if (warp == 1) frag_store(f, merge_buf, lane);
+    named_bar_sync(1, kConsumerWarps * 32);
+    if (warp == 0) {
+      frag_merge(f, merge_buf, lane);
+      const bool complete = seg_start >= g_begin && seg_end <= g_end;
+      if (complete) {
+        frag_write_out<kBf16>(f, a, si.qtok, h, lane);
+      } else {
+        const int slot = seg_start <= g_begin ? 0 : 1;
+        frag_store(f, a.partial + (static_cast<long long>(blockIdx.x) * 2 + slot) * kPartialFloats,
+                   lane);
+      }
+    }
+  };
+
+  bool ok = true;
+  int it = 0;
+  for (int gi = g_begin; gi < g_end; ++gi, ++it) {
+    const int s = it % kStages;
+    const uint32_t ph = (it / kStages) & 1;
+    if (!mbar_wait_bounded(&full_bar[s], ph) || *((volatile int*)&abort_flag)) {
+      ok = false;
+      break;
+    }
+    const uint32_t st = smem_u32(stages + s * kStageBytes);
+    const int tok0 = (si.tile0 + t) * kTile + warp * 16;
+    if (tok0 + 16 > si.lo && tok0 < si.ctx) {
+      // ---- S = Q K^T for 16 tokens: two n-tiles of 8 tokens
+      float sacc[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+      {
+        const int mi = lane >> 3;
+        const int r = lane & 7;
+        const int token = warp * 16 + (mi >> 1) * 8 + r;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const int chunk = ks * 2 + (mi & 1);
+          uint32_t kf[4];
+          ldmatrix_x4(kf, st + (chunk >> 3) * kBoxBytes + swz128(token, chunk & 7));
+          const uint32_t afrag[4] = {qa[ks][0], 0u, qa[ks][1], 0u};
+          mma_16816<kBf16>(sacc[0], afrag, kf[0], kf[1]);
+          mma_16816<kBf16>(sacc[1], afrag, kf[2], kf[3]);
+        }
+      }
+      // ---- online softmax on row g (values sacc[j][0..1]; rows 8..15 unused)
+      float p[2][2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int tok = tok0 + j * 8 + c * 2 + e;
+          const float v = sacc[j][e] * a.scale_log2;
+          p[j][e] = (tok >= si.lo && tok < si.ctx) ? v : -INFINITY;
+        }
+      }
+      float mx = fmaxf(fmaxf(p[0][0], p[0][1]), fmaxf(p[1][0], p[1][1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float mn = fmaxf(f.m, mx);
+      const float mu = mn == -INFINITY ? 0.f : mn;
+      const float alpha = fast_exp2(f.m - mu);
+      f.m = mn;
+      float psum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          p[j][e] = fast_exp2(p[j][e] - mu);
+          psum += p[j][e];
+        }
+      }
+      f.l = f.l * alpha + psum;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        f.o[j][0] *= alpha;
+        f.o[j][1] *= alpha;
+      }
+      // ---- O += P V
+      const uint32_t pfrag[4] = {pack2<kBf16>(p[0][0], p[0][1]), 0u, pack2<kBf16>(p[1][0], p[1][1]),
+                                 0u};
+      {
+        const int mi = lane >> 3;
+        const int r = lane & 7;
+        const int token = warp * 16 + (mi & 1) * 8 + r;
+#pragma unroll
+        for (int jn = 0; jn < 16; jn += 2) {
+          const int chunk = jn + (mi >> 1);
+          uint32_t vf[4];
+          ldmatrix_x4_trans(vf, st + (2 + (chunk >> 3)) * kBoxBytes + swz128(token, chunk & 7));
+          mma_16816_top<kBf16>(f.o[jn], pfrag, vf[0], vf[1]);
+          mma_16816_top<kBf16>(f.o[jn + 1], pfrag, vf[2], vf[3]);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[s]);
+
+    // ---- advance to the next tile; close the segment when it ends
+    ++t;
+    if (t == si.ntiles) {
+      flush(gi + 1);
+      frag_reset(f);
+      t = 0;
+      seg_start = gi + 1;
+      ++h;
+      if (h == a.hkv) {
+        h = 0;
+        if (gi + 1 < g_end) {
+          do {
+            ++b;
+            si = seq_info(a, b);
+          } while (si.ntiles == 0 && b + 1 < a.batch);
+        }
+      }
+      if (gi + 1 < g_end) load_q();
+    }
+  }
+  if (ok && t > 0) flush(seg_start + si.ntiles);
+  if (!ok && lane == 0) atomicOr(a.status, DEV_WAIT_TIMEOUT);
+}
+
+// One warp per (KV head, sequence): merge the partials that the persistent CTAs
+// left for this segment, in CTA order, and write the result.  Also writes zeros
+// for decode sequences without any key.
+template <bool kBf16>
+__global__ void decode_combine_kernel(const DecodeArgs a, int grid_main) {
+  const int lane = threadIdx.x & 31;
+  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (warp_global >= a.batch * a.hkv) return;
+  const int b = warp_global / a.hkv;
+  const int h = warp_global - b * a.hkv;
+  const int q0 = a.cu_q[b];
+  if (a.cu_q[b + 1] - q0 != 1) return;
+  const int nt = (a.prefix[b + 1] - a.prefix[b]) / a.hkv;
+  Frag f;
+  frag_reset(f);
+  if (nt == 0) {
+    frag_write_out<kBf16>(f, a, q0, h, lane);
+    return;
+  }
+  const int total = a.prefix[a.batch];
+  const int per = (total + grid_main - 1) / grid_main;
+  const int s0 = a.prefix[b] + h * nt;
+  const int s1 = s0 + nt;
+  const int c_first = s0 / per;
+  const int c_last = (s1 - 1) / per;
+  if (c_first == c_last) return;  // written directly by its CTA
+  for (int cta = c_first; cta <= c_last; ++cta) {
+    const int slot = s0 <= cta * per ? 0 : 1;
+    frag_merge(f, a.partial + (static_cast<long long>(cta) * 2 + slot) * kPartialFloats, lane);
+  }
+  frag_write_out<kBf16>(f, a, q0, h, lane);
+}
+
+}  // namespace
+
+size_t decode_smem_bytes(int batch) {
+  return static_cast<size_t>(kStages) * kStageBytes + 2 * kPartialFloats * sizeof(float) +
+         2 * kStages * sizeof(uint64_t) + (static_cast<size_t>(batch) + 1) * sizeof(int);
+}
+
+size_t decode_workspace_bytes(int batch) {
+  const size_t prefix_bytes = ((static_cast<size_t>(batch) + 1) * sizeof(int) + 255) / 256 * 256;
+  return prefix_bytes + static_cast<size_t>(kMaxDecodeCtas) * 2 * kPartialFloats * sizeof(float);
+}
+
+int launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, DecodeArgs a, bool bf16,
+                  void* workspace, cudaStream_t stream) {
+  const size_t prefix_bytes = ((static_cast<size_t>(a.batch) + 1) * sizeof(int) + 255) / 256 * 256;
+  a.prefix = static_cast<int*>(workspace);
+  a.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + prefix_bytes);
+  const size_t smem = decode_smem_bytes(a.batch);
+  if (smem > 110 * 1024) {
+    set_error("paged_attn: batch %d too large for the decode scheduler", a.batch);
+    return CWM_ERR_UNSUPPORTED;
+  }
+  int grid = 2 * sm_count();
+  if (grid > kMaxDecodeCtas) grid = kMaxDecodeCtas;
+  static bool attr_set[2] = {false, false};
+  auto main_k = bf16 ? decode_kernel<true> : decode_kernel<false>;
+  if (!attr_set[bf16 ? 1 : 0]) {
+    CWM_CUDA_CHECK(cudaFuncSetAttribute(main_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        110 * 1024));
+    attr_set[bf16 ? 1 : 0] = true;
+  }
+  main_k<<<grid, kThreads, smem, stream>>>(kmap, vmap, a);
+  CWM_CUDA_CHECK(cudaGetLastError());
+  const int warps = a.batch * a.hkv;
+  const int cthreads = 128;
+  const int cgrid = (warps * 32 + cthreads - 1) / cthreads;
+  if (bf16) {
+    decode_combine_kernel<true><<<cgrid, cthreads, 0, stream>>>(a, grid);
+  } else {
+    decode_combine_kernel<false><<<cgrid, cthreads, 0, stream>>>(a, grid);
+  }
+  CWM_CUDA_CHECK(cudaGetLastError());
+  return CWM_OK;
+}
+
+}  // namespace cwm

@@ -1,0 +1,506 @@
+// HBM-bound helpers of the attention path: paged row scatter, rotary embedding,
+// RMS normalisation, and the fused rotate + page-write step.  All are plain
+// coalesced 16-byte load/store kernels; none needs scratch memory.
+#include "common.cuh"
+
+namespace cwm {
+namespace {
+
+__device__ __forceinline__ long long load_batch_size(const void* p, int is_i64) {
+  if (p == nullptr) return 0x7fffffffffffffffLL;
+  return is_i64 ? *reinterpret_cast<const long long*>(p)
+                : static_cast<long long>(*reinterpret_cast<const int*>(p));
+}
+
+// Destination row of token `n`, or -1 when the token is skipped.
+// Addressing of cwm/fastgen/kernels/paged_memcpy.py:56-81, in 64-bit.
+__device__ __forceinline__ long long paged_row(long long n, const int32_t* page_tbl,
+                                               const int32_t* dst_pos, const int32_t* src_batch,
+                                               long long batch_size, int page_size,
+                                               long long tbl_stride, long long tbl_cols,
+                                               long long dst_rows, int shard_idx, int shard_cnt,
+                                               int* status) {
+  if (n >= batch_size) return -1;
+  int pos = dst_pos[n];
+  if (pos < 0) return -1;  // padded lanes carry position -1
+  if (shard_cnt > 1) {
+    if (pos % shard_cnt != shard_idx) return -1;
+    pos /= shard_cnt;
+  }
+  const long long b = src_batch ? static_cast<long long>(src_batch[n]) : n;
+  const long long col = pos / page_size;
+  if (col >= tbl_cols || b < 0) {
+    atomicOr(status, DEV_BAD_POS);
+    return -1;
+  }
+  const long long page = page_tbl[b * tbl_stride + col];
+  const long long row = page * page_size + pos % page_size;
+  if (page < 0 || row >= dst_rows) {
+    atomicOr(status, DEV_BAD_PAGE);
+    return -1;
+  }
+  return row;
+}
+
+// ---------------------------------------------------------------- paged_memcpy
+// One group of `tpr` threads per source row; VecT is the widest type that the
+// row size, strides and base addresses allow.
+template <typename VecT>
+__global__ void paged_memcpy_kernel(const VecT* __restrict__ src, VecT* __restrict__ dst,
+                                    const int32_t* __restrict__ page_tbl,
+                                    const int32_t* __restrict__ dst_pos,
+                                    const int32_t* __restrict__ src_batch, const void* batch_size_p,
+                                    int batch_size_is_i64, long long n_rows, long long row_vecs,
+                                    int page_size, long long tbl_stride, long long tbl_cols,
+                                    long long dst_stride_vecs, long long dst_rows, int shard_idx,
+                                    int shard_cnt, int tpr, int* status) {
+  const long long batch_size = load_batch_size(batch_size_p, batch_size_is_i64);
+  const int rows_per_block = blockDim.x / tpr;
+  const int sub = threadIdx.x / tpr;
+  const int lane = threadIdx.x % tpr;
+  for (long long n = static_cast<long long>(blockIdx.x) * rows_per_block + sub; n < n_rows;
+       n += static_cast<long long>(gridDim.x) * rows_per_block) {
+    const long long row = paged_row(n, page_tbl, dst_pos, src_batch, batch_size, page_size,
+                                    tbl_stride, tbl_cols, dst_rows, shard_idx, shard_cnt, status);
+    if (row < 0) continue;
+    const VecT* s = src + n * row_vecs;
+    VecT* d = dst + row * dst_stride_vecs;
+    for (long long i = lane; i < row_vecs; i += tpr) d[i] = s[i];
+  }
+}
+
+template <typename VecT>
+int launch_paged_memcpy(const void* src, void* dst, const int32_t* page_tbl,
+                        const int32_t* dst_pos, const int32_t* src_batch, const void* batch_size,
+                        int is_i64, int64_t n, int64_t row_bytes, int page_size,
+                        int64_t tbl_stride, int64_t tbl_cols, int64_t dst_stride_bytes,
+                        int64_t dst_rows, int shard_idx, int shard_cnt, cudaStream_t stream) {
+  const long long row_vecs = row_bytes / sizeof(VecT);
+  int tpr = 1;
+  while (tpr < 256 && tpr < row_vecs) tpr <<= 1;
+  const int threads = 256;
+  const int rows_per_block = threads / tpr;
+  long long blocks = (n + rows_per_block - 1) / rows_per_block;
+  const long long max_blocks = static_cast<long long>(sm_count()) * 16;
+  if (blocks > max_blocks) blocks = max_blocks;
+  paged_memcpy_kernel<VecT><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+      static_cast<const VecT*>(src), static_cast<VecT*>(dst), page_tbl, dst_pos, src_batch,
+      batch_size, is_i64, n, row_vecs, page_size, tbl_stride, tbl_cols,
+      dst_stride_bytes / static_cast<long long>(sizeof(VecT)), dst_rows, shard_idx, shard_cnt, tpr,
+      status_word());
+  CWM_CUDA_CHECK(cudaGetLastError());
+  return CWM_OK;
+}
+
+// ------------------------------------------------------------------------ rope
+template <typename T>
+struct Vec16 {
+  static constexpr int kElems = 16 / sizeof(T);
+  uint4 raw;
+};
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+// Rotates the kElems/2 pairs held in one 16-byte vector.  cs holds (cos, sin)
+// per pair.  Formula of cwm/fastgen/kernels/rope.py:84-85.
+template <typename T>
+__device__ __forceinline__ uint4 rotate_vec(uint4 raw, const float2* cs) {
+  constexpr int kE = 16 / sizeof(T);
+  T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < kE / 2; ++i) {
+    const float re = to_f32(e[2 * i]);
+    const float im = to_f32(e[2 * i + 1]);
+    // products and sum as separate roundings, like the reference's fp32 math
+    const float o_re = __fsub_rn(__fmul_rn(re, cs[i].x), __fmul_rn(im, cs[i].y));
+    const float o_im = __fadd_rn(__fmul_rn(im, cs[i].x), __fmul_rn(re, cs[i].y));
+    e[2 * i] = from_f32<T>(o_re);
+    e[2 * i + 1] = from_f32<T>(o_im);
+  }
+  return raw;
+}
+
+// (cos, sin) of the pairs covered by vector `v` of a head, for position `pos`.
+template <typename T>
+__device__ __forceinline__ void pair_cos_sin(int pos, int v, const float* __restrict__ freqs,
+                                             float2* cs) {
+  constexpr int kP = 8 / sizeof(T);  // pairs per 16-byte vector
+  const float fpos = static_cast<float>(pos);
+#pragma unroll
+  for (int i = 0; i < kP; ++i) {
+    const float a = __fmul_rn(fpos, freqs[v * kP + i]);  // rope.py:58
+    cs[i].x = cosf(a);
+    cs[i].y = sinf(a);
+  }
+}
+
+// One block per token.  Thread (hslot, v) owns vector v of heads hslot,
+// hslot + slots, ...; cos/sin are computed once per thread and reused.
+template <typename T>
+__global__ void rope_kernel(uint4* __restrict__ x, const int32_t* __restrict__ pos,
+                            const float* __restrict__ freqs, int n_heads, int vecs_per_head) {
+  constexpr int kP = 8 / sizeof(T);
+  const long long n = blockIdx.x;
+  const int v = threadIdx.x % vecs_per_head;
+  const int hslot = threadIdx.x / vecs_per_head;
+  const int slots = blockDim.x / vecs_per_head;
+  if (hslot >= slots) return;
+  float2 cs[kP];
+  pair_cos_sin<T>(pos[n], v, freqs, cs);
+  uint4* row = x + n * n_heads * vecs_per_head;
+  for (int h = hslot; h < n_heads; h += slots) {
+    uint4* p = row + h * vecs_per_head + v;
+    *p = rotate_vec<T>(*p, cs);
+  }
+}
+
+// ----------------------------------------------------- fused rope + page write
+template <typename T>
+__global__ void rope_kv_write_kernel(uint4* __restrict__ xq, uint4* __restrict__ xk,
+                                     const uint4* __restrict__ xv, uint4* __restrict__ cache_k,
+                                     uint4* __restrict__ cache_v, const int32_t* __restrict__ pos,
+                                     const float* __restrict__ freqs,
+                                     const int32_t* __restrict__ page_tbl,
+                                     const int32_t* __restrict__ src_batch,
+                                     const void* batch_size_p, int batch_size_is_i64, int hq,
+                                     int hkv, int vecs_per_head, int page_size,
+                                     long long tbl_stride, long long tbl_cols,
+                                     long long cache_stride_vecs, long long cache_rows,
+                                     int* status) {
+  constexpr int kP = 8 / sizeof(T);
+  const long long n = blockIdx.x;
+  const int v = threadIdx.x % vecs_per_head;
+  const int hslot = threadIdx.x / vecs_per_head;
+  const int slots = blockDim.x / vecs_per_head;
+  if (hslot >= slots) return;
+  float2 cs[kP];
+  pair_cos_sin<T>(pos[n], v, freqs, cs);
+  const long long batch_size = load_batch_size(batch_size_p, batch_size_is_i64);
+  const long long row = paged_row(n, page_tbl, pos, src_batch, batch_size, page_size, tbl_stride,
+                                  tbl_cols, cache_rows, 0, 1, status);
+  if (xq != nullptr) {
+    uint4* qrow = xq + n * hq * vecs_per_head;
+    for (int h = hslot; h < hq; h += slots) {
+      uint4* p = qrow + h * vecs_per_head + v;
+      *p = rotate_vec<T>(*p, cs);
+    }
+  }
+  uint4* krow = xk + n * hkv * vecs_per_head;
+  const uint4* vrow = xv + n * hkv * vecs_per_head;
+  for (int h = hslot; h < hkv; h += slots) {
+    const int idx = h * vecs_per_head + v;
+    const uint4 kr = rotate_vec<T>(krow[idx], cs);
+    krow[idx] = kr;
+    if (row >= 0) {
+      cache_k[row * cache_stride_vecs + idx] = kr;
+      cache_v[row * cache_stride_vecs + idx] = vrow[idx];
+    }
+  }
+}
+
+// --------------------------------------------------------------------- rmsnorm
+// One block per row; the row stays in registers between the sum of squares and
+// the scaling, so HBM sees one read and one write per element.
+template <typename T, int kVpt>
+__global__ void rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w,
+                               uint4* __restrict__ out, int row_vecs, float inv_d, float eps) {
+  constexpr int kE = 16 / sizeof(T);
+  const long long n = blockIdx.x;
+  const uint4* xr = x + n * row_vecs;
+  uint4 regs[kVpt];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kVpt; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < row_vecs) {
+      regs[i] = xr[idx];
+      const T* e = reinterpret_cast<const T*>(&regs[i]);
+#pragma unroll
+      for (int j = 0; j < kE; ++j) {
+        const float a = to_f32(e[j]);
+        ss = fmaf(a, a, ss);
+      }
+    }
+  }
+  __shared__ float warp_sums[32];
+  __shared__ float rstd_s;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? warp_sums[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) rstd_s = rsqrtf(t * inv_d + eps);
+  }
+  __syncthreads();
+  const float rstd = rstd_s;
+  uint4* orow = out + n * row_vecs;
+#pragma unroll
+  for (int i = 0; i < kVpt; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < row_vecs) {
+      const uint4 wv = w[idx];
+      const T* we = reinterpret_cast<const T*>(&wv);
+      T* e = reinterpret_cast<T*>(&regs[i]);
+#pragma unroll
+      for (int j = 0; j < kE; ++j) {
+        // (a * rstd) * w, cwm/fastgen/kernels/rmsnorm.py:61
+        e[j] = from_f32<T>(__fmul_rn(__fmul_rn(to_f32(e[j]), rstd), to_f32(we[j])));
+      }
+      orow[idx] = regs[i];
+    }
+  }
+}
+
+// Any row length and alignment: scalar loads, two passes (the second pass hits L2).
+template <typename T>
+__global__ void rmsnorm_generic_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                       T* __restrict__ out, int d, float inv_d, float eps) {
+  const long long n = blockIdx.x;
+  const T* xr = x + n * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float a = to_f32(xr[i]);
+    ss = fmaf(a, a, ss);
+  }
+  __shared__ float warp_sums[32];
+  __shared__ float rstd_s;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? warp_sums[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) rstd_s = rsqrtf(t * inv_d + eps);
+  }
+  __syncthreads();
+  const float rstd = rstd_s;
+  T* orow = out + n * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    orow[i] = from_f32<T>(__fmul_rn(__fmul_rn(to_f32(xr[i]), rstd), to_f32(w[i])));
+  }
+}
+
+template <typename T>
+int launch_rmsnorm(const void* x, const void* w, void* out, int64_t n, int d, float eps,
+                   cudaStream_t stream) {
+  const float inv_d = 1.0f / static_cast<float>(d);
+  const int64_t row_bytes = static_cast<int64_t>(d) * sizeof(T);
+  const bool vec_ok = row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+                      reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
+                      reinterpret_cast<uintptr_t>(out) % 16 == 0;
+  const int row_vecs = static_cast<int>(row_bytes / 16);
+  const unsigned grid = static_cast<unsigned>(n);
+  if (vec_ok && row_vecs <= 256 * 8) {
+    const int threads = row_vecs >= 512 ? 256 : 128;
+    const int vpt = (row_vecs + threads - 1) / threads;
+    auto xs = static_cast<const uint4*>(x);
+    auto ws = static_cast<const uint4*>(w);
+    auto os = static_cast<uint4*>(out);
+#define CWM_RMS_CASE(V)                                                                       \
+  case V:                                                                                     \
+    rmsnorm_kernel<T, V><<<grid, threads, 0, stream>>>(xs, ws, os, row_vecs, inv_d, eps);     \
+    break;
+    switch (vpt) {
+      CWM_RMS_CASE(1)
+      CWM_RMS_CASE(2)
+      CWM_RMS_CASE(3)
+      CWM_RMS_CASE(4)
+      CWM_RMS_CASE(5)
+      CWM_RMS_CASE(6)
+      CWM_RMS_CASE(7)
+      CWM_RMS_CASE(8)
+      default:
+        set_error("rmsnorm: internal vector count %d", vpt);
+        return CWM_ERR_INVALID;
+    }
+#undef CWM_RMS_CASE
+  } else {
+    rmsnorm_generic_kernel<T><<<grid, 256, 0, stream>>>(
+        static_cast<const T*>(x), static_cast<const T*>(w), static_cast<T*>(out), d, inv_d, eps);
+  }
+  CWM_CUDA_CHECK(cudaGetLastError());
+  return CWM_OK;
+}
+
+int rope_threads(int n_heads, int vecs_per_head) {
+  int slots = 256 / vecs_per_head;
+  if (slots > n_heads) slots = n_heads;
+  if (slots < 1) slots = 1;
+  return slots * vecs_per_head;
+}
+
+}  // namespace
+}  // namespace cwm
+
+using namespace cwm;
+
+extern "C" int cwm_paged_memcpy(const void* src, void* dst, const int32_t* page_tbl,
+                                const int32_t* dst_pos, const int32_t* src_batch,
+                                const void* batch_size, int batch_size_is_i64, int64_t n,
+                                int64_t e, int elem_bytes, int page_size, int64_t page_tbl_stride,
+                                int64_t page_tbl_cols, int64_t dst_stride, int64_t dst_rows,
+                                int shard_idx, int shard_cnt, void* stream) {
+  if (n == 0 || e == 0) return CWM_OK;
+  if (!src || !dst || !page_tbl || !dst_pos) {
+    set_error("paged_memcpy: null pointer");
+    return CWM_ERR_INVALID;
+  }
+  if (n < 0 || e < 0 || elem_bytes <= 0 || page_size <= 0 || shard_cnt < 1 || shard_idx < 0 ||
+      shard_idx >= shard_cnt || dst_stride < e || page_tbl_cols < 0) {
+    set_error("paged_memcpy: bad size argument");
+    return CWM_ERR_INVALID;
+  }
+  const int64_t row_bytes = e * elem_bytes;
+  const int64_t stride_bytes = dst_stride * elem_bytes;
+  const uintptr_t align = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) |
+                          static_cast<uintptr_t>(row_bytes) | static_cast<uintptr_t>(stride_bytes);
+  auto st = static_cast<cudaStream_t>(stream);
+#define CWM_MC(V)                                                                              \
+  return launch_paged_memcpy<V>(src, dst, page_tbl, dst_pos, src_batch, batch_size,            \
+                                batch_size_is_i64, n, row_bytes, page_size, page_tbl_stride,   \
+                                page_tbl_cols, stride_bytes, dst_rows, shard_idx, shard_cnt, st)
+  if (align % 16 == 0) CWM_MC(uint4);
+  if (align % 8 == 0) CWM_MC(uint2);
+  if (align % 4 == 0) CWM_MC(uint32_t);
+  if (align % 2 == 0) CWM_MC(uint16_t);
+  CWM_MC(uint8_t);
+#undef CWM_MC
+}
+
+extern "C" int cwm_rope(void* x, const int32_t* pos, const float* freqs, int64_t n, int h, int d,
+                        int dtype, void* stream) {
+  if (n == 0 || h == 0) return CWM_OK;
+  if (!x || !pos || !freqs) {
+    set_error("rope: null pointer");
+    return CWM_ERR_INVALID;
+  }
+  const int esz = dtype == CWM_F32 ? 4 : 2;
+  if (n < 0 || h < 0 || d <= 0 || d % 2 != 0) {
+    set_error("rope: bad size argument");
+    return CWM_ERR_INVALID;
+  }
+  if ((d * esz) % 16 != 0 || reinterpret_cast<uintptr_t>(x) % 16 != 0 || d * esz / 16 > 256) {
+    set_error("rope: head_dim %d (x %d bytes) must make 16-byte aligned heads of at most 4 KiB",
+              d, esz);
+    return CWM_ERR_UNSUPPORTED;
+  }
+  const int vph = d * esz / 16;
+  const int threads = rope_threads(h, vph);
+  auto st = static_cast<cudaStream_t>(stream);
+  auto xv = static_cast<uint4*>(x);
+  const unsigned grid = static_cast<unsigned>(n);
+  switch (dtype) {
+    case CWM_BF16:
+      rope_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(xv, pos, freqs, h, vph);
+      break;
+    case CWM_F16:
+      rope_kernel<__half><<<grid, threads, 0, st>>>(xv, pos, freqs, h, vph);
+      break;
+    case CWM_F32:
+      rope_kernel<float><<<grid, threads, 0, st>>>(xv, pos, freqs, h, vph);
+      break;
+    default:
+      set_error("rope: unknown dtype %d", dtype);
+      return CWM_ERR_UNSUPPORTED;
+  }
+  CWM_CUDA_CHECK(cudaGetLastError());
+  return CWM_OK;
+}
+
+extern "C" int cwm_rmsnorm(const void* x, const void* w, void* out, int64_t n, int d, float eps,
+                           int dtype, void* stream) {
+  if (n == 0) return CWM_OK;
+  if (!x || !w || !out) {
+    set_error("rmsnorm: null pointer");
+    return CWM_ERR_INVALID;
+  }
+  if (n < 0 || d <= 0) {
+    set_error("rmsnorm: bad size argument");
+    return CWM_ERR_INVALID;
+  }
+  auto st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case CWM_BF16:
+      return launch_rmsnorm<__nv_bfloat16>(x, w, out, n, d, eps, st);
+    case CWM_F16:
+      return launch_rmsnorm<__half>(x, w, out, n, d, eps, st);
+    case CWM_F32:
+      return launch_rmsnorm<float>(x, w, out, n, d, eps, st);
+    default:
+      set_error("rmsnorm: unknown dtype %d", dtype);
+      return CWM_ERR_UNSUPPORTED;
+  }
+}
+
+extern "C" int cwm_rope_kv_write(void* xq, void* xk, const void* xv, void* cache_k, void* cache_v,
+                                 const int32_t* pos, const float* freqs, const int32_t* page_tbl,
+                                 const int32_t* src_batch, const void* batch_size,
+                                 int batch_size_is_i64, int64_t t, int hq, int hkv, int d,
+                                 int dtype, int page_size, int64_t page_tbl_stride,
+                                 int64_t page_tbl_cols, int64_t cache_stride, int64_t cache_rows,
+                                 void* stream) {
+  if (t == 0) return CWM_OK;
+  if (!xk || !xv || !cache_k || !cache_v || !pos || !freqs || !page_tbl) {
+    set_error("rope_kv_write: null pointer");
+    return CWM_ERR_INVALID;
+  }
+  const int esz = dtype == CWM_F32 ? 4 : 2;
+  if (t < 0 || hq < 0 || hkv <= 0 || d <= 0 || d % 2 != 0 || page_size <= 0 ||
+      cache_stride < static_cast<int64_t>(hkv) * d) {
+    set_error("rope_kv_write: bad size argument");
+    return CWM_ERR_INVALID;
+  }
+  const uintptr_t align = reinterpret_cast<uintptr_t>(xq) | reinterpret_cast<uintptr_t>(xk) |
+                          reinterpret_cast<uintptr_t>(xv) | reinterpret_cast<uintptr_t>(cache_k) |
+                          reinterpret_cast<uintptr_t>(cache_v) |
+                          static_cast<uintptr_t>(cache_stride * esz) |
+                          static_cast<uintptr_t>(d * esz);
+  if (align % 16 != 0 || d * esz / 16 > 256) {
+    set_error("rope_kv_write: tensors, head size and cache row stride must be 16-byte aligned");
+    return CWM_ERR_UNSUPPORTED;
+  }
+  const int vph = d * esz / 16;
+  const int threads = rope_threads(hq > hkv ? hq : hkv, vph);
+  auto st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(t);
+#define CWM_RKW(T)                                                                              \
+  rope_kv_write_kernel<T><<<grid, threads, 0, st>>>(                                            \
+      static_cast<uint4*>(xq), static_cast<uint4*>(xk), static_cast<const uint4*>(xv),          \
+      static_cast<uint4*>(cache_k), static_cast<uint4*>(cache_v), pos, freqs, page_tbl,         \
+      src_batch, batch_size, batch_size_is_i64, hq, hkv, vph, page_size, page_tbl_stride,       \
+      page_tbl_cols, cache_stride * esz / 16, cache_rows, status_word())
+  switch (dtype) {
+    case CWM_BF16:
+      CWM_RKW(__nv_bfloat16);
+      break;
+    case CWM_F16:
+      CWM_RKW(__half);
+      break;
+    case CWM_F32:
+      CWM_RKW(float);
+      break;
+    default:
+      set_error("rope_kv_write: unknown dtype %d", dtype);
+      return CWM_ERR_UNSUPPORTED;
+  }
+#undef CWM_RKW
+  CWM_CUDA_CHECK(cudaGetLastError());
+  return CWM_OK;
+}

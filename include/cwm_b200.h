@@ -1,0 +1,127 @@
+/*
+ * C ABI of the B200 (sm_100a) implementation of the FastGen attention hot path.
+ *
+ * The reference (facebookresearch/cwm) has no FFI layer of its own: the boundary
+ * of this path is the set of Python call signatures used by
+ * cwm/fastgen/forward.py.  Each entry point below replaces one of them and cites
+ * it.  All pointers are device pointers unless stated otherwise, all tensors are
+ * owned by the caller, nothing here allocates device memory, and every launch
+ * goes to the stream given (a cudaStream_t passed as void*).  Calls are
+ * asynchronous and may be captured in a CUDA graph unless stated otherwise.
+ *
+ * Return value: CWM_OK or a CWM_ERR_* code; cwm_last_error() gives a message for
+ * the calling thread.  Conditions that the kernels detect on the device (a block
+ * id outside the cache, a wait that ran out) are recorded in a status word that
+ * cwm_device_status() reads back.
+ */
+#ifndef CWM_B200_H_
+#define CWM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define CWM_API __attribute__((visibility("default")))
+#else
+#define CWM_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum cwm_status {
+  CWM_OK = 0,
+  CWM_ERR_INVALID = 1,     /* bad argument (shape, stride, alignment, null) */
+  CWM_ERR_UNSUPPORTED = 2, /* valid but not built (head_dim, dtype, group size) */
+  CWM_ERR_CUDA = 3,        /* a CUDA runtime/driver call failed */
+  CWM_ERR_WORKSPACE = 4    /* workspace missing or too small */
+};
+
+enum cwm_dtype { CWM_BF16 = 0, CWM_F16 = 1, CWM_F32 = 2 };
+
+/* Library version (major * 100 + minor). */
+CWM_API int cwm_version(void);
+/* Text for a cwm_status code. */
+CWM_API const char* cwm_strerror(int code);
+/* Detailed message of the last failing call on this thread ("" if none). */
+CWM_API const char* cwm_last_error(void);
+/* Copies the device status word of the current device to *host_out and clears
+ * it.  Synchronises the stream; not for use during graph capture.  Bits:
+ * 1 = block id outside the cache, 2 = bounded wait ran out, 4 = bad position. */
+CWM_API int cwm_device_status(int32_t* host_out, void* stream);
+
+/* In-place rotary embedding on x[N, H, D] (interleaved pairs, fp32 math).
+ * Replaces apply_rope(x, pos, freqs), cwm/fastgen/kernels/rope.py:93-163.
+ * pos: int32[N]; freqs: float32[D/2]. */
+CWM_API int cwm_rope(void* x, const int32_t* pos, const float* freqs, int64_t n, int h, int d, int dtype,
+             void* stream);
+
+/* out[N, D] = (x * rsqrt(mean(x^2) + eps)) * w, fp32 accumulation.
+ * Replaces rmsnorm(x, w, eps), cwm/fastgen/kernels/rmsnorm.py:64-119 (and the
+ * rms_norm calls of cwm/fastgen/forward.py:571,772,789).  x, w, out share dtype. */
+CWM_API int cwm_rmsnorm(const void* x, const void* w, void* out, int64_t n, int d, float eps, int dtype,
+                void* stream);
+
+/* Scatter rows src[N, E] into a paged destination through a block table.
+ * Replaces paged_memcpy(...), cwm/fastgen/kernels/paged_memcpy.py:90-228.
+ * Row n goes to dst row page_tbl[b, pos / page_size] * page_size + pos % page_size
+ * with b = src_batch[n] (n if null) and pos = dst_pos[n]; rows n >= *batch_size
+ * are skipped when batch_size is given (an int32 or int64 device scalar).  With
+ * shard_cnt > 1 only pos % shard_cnt == shard_idx is stored, at pos / shard_cnt.
+ * Strides are in elements.  dst_rows bounds the destination: a row outside it is
+ * not written and sets status bit 1. */
+CWM_API int cwm_paged_memcpy(const void* src, void* dst, const int32_t* page_tbl, const int32_t* dst_pos,
+                     const int32_t* src_batch /* nullable */, const void* batch_size /* nullable */,
+                     int batch_size_is_i64, int64_t n, int64_t e, int elem_bytes, int page_size,
+                     int64_t page_tbl_stride, int64_t page_tbl_cols, int64_t dst_stride,
+                     int64_t dst_rows, int shard_idx, int shard_cnt, void* stream);
+
+/* Fused form of the four calls at cwm/fastgen/forward.py:618-632: rotate
+ * xq[T, Hq, D] and xk[T, Hkv, D] in place, then store the rotated k rows and the
+ * xv rows into cache_k / cache_v (row stride cache_stride elements, heads
+ * contiguous in a row) at the paged position of each token.  Same addressing and
+ * batch_size rule as cwm_paged_memcpy (the rotation itself is unconditional, as
+ * in the reference).  xq may be null (k/v only). */
+CWM_API int cwm_rope_kv_write(void* xq, void* xk, const void* xv, void* cache_k, void* cache_v,
+                      const int32_t* pos, const float* freqs, const int32_t* page_tbl,
+                      const int32_t* src_batch /* nullable */,
+                      const void* batch_size /* nullable */, int batch_size_is_i64, int64_t t,
+                      int hq, int hkv, int d, int dtype, int page_size, int64_t page_tbl_stride,
+                      int64_t page_tbl_cols, int64_t cache_stride, int64_t cache_rows,
+                      void* stream);
+
+/* Bytes of scratch that cwm_paged_attn_fwd needs for this problem size (split-KV
+ * partial results and scheduling prefixes).  Depends on static sizes only. */
+CWM_API size_t cwm_paged_attn_workspace_bytes(int batch, int64_t total_q, int hq, int hkv, int d);
+
+/* Variable-length paged-KV grouped-query attention, causal, with an optional
+ * sliding window.  Replaces the call
+ *   mha_fwd(query, key, value, cu_seqlens_q, None, seqused_k, None, max_seqlen_q,
+ *           max_seqlen_k, 0, block_table, softmax_scale, True, window_left, -1)
+ * at cwm/fastgen/forward.py:639-655 (xformers.ops.fmha.flash3.mha_fwd).
+ *
+ * q, out: [total_q, hq, d], contiguous.  k, v: element (page, tok, head, :) lives
+ * at base + ((page * page_size + tok) * kv_token_stride + head * d) elements,
+ * i.e. the strided views FastGen makes of its [K|V] cache rows.  Sequence b has
+ * queries cu_seqlens_q[b] .. cu_seqlens_q[b+1] and seqused_k[b] keys; query j of
+ * t sits at position seqused_k[b] - t + j and sees keys
+ * max(0, pos - window_left) .. pos (window_left < 0: from 0).  Query head h uses
+ * KV head h / (hq / hkv).  block_table: int32 [batch, *] with row stride
+ * bt_stride; only the first ceil(seqused_k[b] / page_size) entries of a row are
+ * read.  lse (nullable): float32 [hq, total_q], natural log.  All lengths are
+ * read on the device, so the launch is valid for any lengths within the static
+ * bounds max_seqlen_q / max_seqlen_k.  Sequences with one query are served by
+ * the split-KV decode kernel, the others by the tensor-core prefill kernel. */
+CWM_API int cwm_paged_attn_fwd(const void* q, const void* k, const void* v, void* out,
+                       float* lse /* nullable */, const int32_t* cu_seqlens_q,
+                       const int32_t* seqused_k, const int32_t* block_table, int batch,
+                       int64_t total_q, int hq, int hkv, int d, int dtype, int page_size,
+                       int64_t num_pages, int64_t kv_token_stride, int64_t bt_stride,
+                       int max_seqlen_q, int max_seqlen_k, float softmax_scale, int window_left,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CWM_B200_H_ */
