@@ -209,7 +209,8 @@ def test_mha_fwd_rejects_what_is_not_built(ops):
                 window_right=-1)
     for bad in (dict(is_causal=False), dict(p=0.1), dict(cu_seqlens_k=p.cu_seqlens_q),
                 dict(query=p.q.float()), dict(seqused_k=p.seqused_k.long()),
-                dict(block_table=p.block_table.long()), dict(query=p.q[:, :5])):
+                dict(block_table=p.block_table.long()), dict(query=p.q[:, :, ::2]),
+                dict(key=k4[:, :, :, ::2])):
         with pytest.raises(ValueError):
             ops.mha_fwd(**{**args, **bad})
     d64 = make_problem([1], [10], hq=2, hkv=1, d=64, seed=0).to(DEV)
