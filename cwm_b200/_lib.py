@@ -49,6 +49,12 @@ SIGNATURES: dict[str, tuple] = {
          c_int64, c_int, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int,
          c_float, c_int, c_void_p, c_size_t, c_void_p],
     ),
+    "cwm_paged_attn_decode_noalloc": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+         c_int, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_float, c_int,
+         c_void_p],
+    ),
 }
 
 _lib: ctypes.CDLL | None = None

@@ -38,8 +38,11 @@ struct AttnArgs {
 using DecodeArgs = AttnArgs;
 
 size_t decode_workspace_bytes(int batch);
+// max_ctas caps the persistent grid (the workspace holds two partials per CTA).
 int launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, AttnArgs a, bool bf16,
-                  void* workspace, cudaStream_t stream);
+                  void* workspace, cudaStream_t stream, int max_ctas = kMaxDecodeCtas);
+// Workspace bytes for a decode grid of at most max_ctas CTAs.
+size_t decode_workspace_bytes_for(int batch, int max_ctas);
 int launch_prefill(const CUtensorMap& kmap, const CUtensorMap& vmap, AttnArgs a, bool bf16,
                    cudaStream_t stream);
 

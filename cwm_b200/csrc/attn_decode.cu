@@ -446,13 +446,17 @@ size_t decode_smem_bytes(int batch) {
          2 * kStages * sizeof(uint64_t) + (static_cast<size_t>(batch) + 1) * sizeof(int);
 }
 
-size_t decode_workspace_bytes(int batch) {
+size_t decode_workspace_bytes_for(int batch, int max_ctas) {
   const size_t prefix_bytes = ((static_cast<size_t>(batch) + 1) * sizeof(int) + 255) / 256 * 256;
-  return prefix_bytes + static_cast<size_t>(kMaxDecodeCtas) * 2 * kPartialFloats * sizeof(float);
+  return prefix_bytes + static_cast<size_t>(max_ctas) * 2 * kPartialFloats * sizeof(float);
+}
+
+size_t decode_workspace_bytes(int batch) {
+  return decode_workspace_bytes_for(batch, kMaxDecodeCtas);
 }
 
 int launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, DecodeArgs a, bool bf16,
-                  void* workspace, cudaStream_t stream) {
+                  void* workspace, cudaStream_t stream, int max_ctas) {
   const size_t prefix_bytes = ((static_cast<size_t>(a.batch) + 1) * sizeof(int) + 255) / 256 * 256;
   a.prefix = static_cast<int*>(workspace);
   a.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + prefix_bytes);
@@ -462,7 +466,7 @@ int launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, DecodeArgs a
     return CWM_ERR_UNSUPPORTED;
   }
   int grid = 2 * sm_count();
-  if (grid > kMaxDecodeCtas) grid = kMaxDecodeCtas;
+  if (grid > max_ctas) grid = max_ctas;
   static bool attr_set[2] = {false, false};
   auto main_k = bf16 ? decode_kernel<true> : decode_kernel<false>;
   if (!attr_set[bf16 ? 1 : 0]) {

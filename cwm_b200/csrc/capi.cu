@@ -288,3 +288,142 @@ extern "C" int cwm_paged_attn_fwd(const void* q, const void* k, const void* v, v
   }
   return CWM_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate device memory.
+//
+// Some embedders of this library run where cudaMalloc is off the table: inside a
+// serving loop whose memory is fully pre-planned, in a plugin that is handed
+// fixed buffers by its host, or on a thread that must never block on the
+// allocator.  They can still pass their own q / cache / output buffers, but they
+// have nowhere to get the split-KV scratch from.  For them the scratch lives in
+// the library image itself.
+namespace cwm {
+namespace {
+
+// Sized for kNoAllocMaxBatch sequences and a persistent grid of kNoAllocMaxCtas
+// CTAs (two per SM on a 148-SM B200, with headroom to 152 SMs): about 2.6 MB
+// that every GPU holds from the moment it loads the library until exit.
+constexpr int kNoAllocMaxBatch = CWM_NOALLOC_MAX_BATCH;
+constexpr int kNoAllocMaxCtas = 304;
+constexpr size_t kNoAllocScratchBytes =
+    ((static_cast<size_t>(kNoAllocMaxBatch) + 1) * sizeof(int) + 255) / 256 * 256 +
+    static_cast<size_t>(kNoAllocMaxCtas) * 2 * 34 * 32 * sizeof(float);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+// Device address of the scratch array on the current device.  In host code the
+// array's name is only a handle; the address the kernels need comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+int noalloc_scratch(void** out) {
+  static void* ptrs[kMaxDevices] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  CWM_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    set_error("paged_attn_decode_noalloc: device index %d out of range", dev);
+    return CWM_ERR_UNSUPPORTED;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    CWM_CUDA_CHECK(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return CWM_OK;
+}
+
+}  // namespace
+}  // namespace cwm
+
+extern "C" int cwm_paged_attn_decode_noalloc(const void* q, const void* k, const void* v,
+                                             void* out, float* lse,
+                                             const int32_t* cu_seqlens_q,
+                                             const int32_t* seqused_k,
+                                             const int32_t* block_table, int batch, int hq,
+                                             int hkv, int d, int dtype, int page_size,
+                                             int64_t num_pages, int64_t kv_token_stride,
+                                             int64_t bt_stride, int max_seqlen_k,
+                                             float softmax_scale, int window_left,
+                                             void* stream) {
+  if (batch == 0) return CWM_OK;
+  if (!q || !k || !v || !out || !cu_seqlens_q || !seqused_k || !block_table) {
+    set_error("paged_attn_decode_noalloc: null pointer");
+    return CWM_ERR_INVALID;
+  }
+  if (batch < 0 || batch > kNoAllocMaxBatch) {
+    set_error("paged_attn_decode_noalloc: batch %d exceeds the built-in scratch (at most %d "
+              "sequences per call)", batch, kNoAllocMaxBatch);
+    return CWM_ERR_WORKSPACE;
+  }
+  if (hq <= 0 || hkv <= 0 || hq % hkv != 0 || page_size <= 0 || num_pages <= 0 ||
+      max_seqlen_k < 0 || bt_stride < 0 || kv_token_stride < static_cast<int64_t>(hkv) * d) {
+    set_error("paged_attn_decode_noalloc: bad size argument");
+    return CWM_ERR_INVALID;
+  }
+  if (d != kHeadDim || (dtype != CWM_BF16 && dtype != CWM_F16) || hq / hkv > 8 ||
+      page_size % 64 != 0) {
+    set_error("paged_attn_decode_noalloc: only head_dim 128, bf16/fp16, at most 8 query heads "
+              "per KV head and page sizes that are multiples of 64 are built");
+    return CWM_ERR_UNSUPPORTED;
+  }
+  const uintptr_t align = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+                          reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out) |
+                          static_cast<uintptr_t>(kv_token_stride * 2);
+  if (align % 16 != 0) {
+    set_error("paged_attn_decode_noalloc: q, k, v, out and the K/V token stride must be "
+              "16-byte aligned");
+    return CWM_ERR_INVALID;
+  }
+  if (num_pages * page_size > 0x7fffffffLL) {
+    set_error("paged_attn_decode_noalloc: cache of %lld rows is too large",
+              (long long)(num_pages * page_size));
+    return CWM_ERR_UNSUPPORTED;
+  }
+  void* scratch = nullptr;
+  int rc = noalloc_scratch(&scratch);
+  if (rc != CWM_OK) return rc;
+  if (decode_workspace_bytes_for(batch, kNoAllocMaxCtas) > kNoAllocScratchBytes) {
+    set_error("paged_attn_decode_noalloc: internal scratch sizing error");
+    return CWM_ERR_WORKSPACE;
+  }
+  int* status = status_word();
+  if (status == nullptr) {
+    set_error("paged_attn_decode_noalloc: cannot resolve the device status word");
+    return CWM_ERR_CUDA;
+  }
+  CUtensorMap kmap, vmap;
+  const long long inner = static_cast<long long>(hkv) * d;
+  const long long rows = num_pages * page_size;
+  rc = get_kv_map(k, inner, rows, kv_token_stride * 2, dtype, 64, &kmap);
+  if (rc != CWM_OK) return rc;
+  rc = get_kv_map(v, inner, rows, kv_token_stride * 2, dtype, 64, &vmap);
+  if (rc != CWM_OK) return rc;
+
+  AttnArgs a;
+  memset(&a, 0, sizeof(a));
+  a.q = q;
+  a.out = out;
+  a.lse = lse;
+  a.cu_q = cu_seqlens_q;
+  a.seq_k = seqused_k;
+  a.block_table = block_table;
+  a.batch = batch;
+  a.hq = hq;
+  a.hkv = hkv;
+  a.group = hq / hkv;
+  a.page_size = page_size;
+  a.max_seqlen_q = 1;
+  a.max_seqlen_k = max_seqlen_k;
+  a.num_pages = num_pages;
+  a.bt_stride = bt_stride;
+  a.total_q = batch;
+  a.scale_log2 = softmax_scale * 1.4426950408889634f;
+  a.window_left = window_left;
+  a.status = status;
+  // Nothing in the scratch has to start at zero: the tile prefix is rewritten in
+  // full by every launch, and the combine step reads only the partial slots that
+  // this launch wrote.
+  return launch_decode(kmap, vmap, a, dtype == CWM_BF16, scratch,
+                       static_cast<cudaStream_t>(stream), kNoAllocMaxCtas);
+}

@@ -121,6 +121,35 @@ CWM_API int cwm_paged_attn_fwd(const void* q, const void* k, const void* v, void
                        int max_seqlen_q, int max_seqlen_k, float softmax_scale, int window_left,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* Largest batch cwm_paged_attn_decode_noalloc accepts. */
+#define CWM_NOALLOC_MAX_BATCH 1024
+
+/* Decode attention (one query per sequence) without any caller-provided scratch.
+ * No counterpart in the reference: it exists for embedders that cannot allocate
+ * device memory at call time -- a host application that hands a plugin a fixed
+ * set of buffers, a serving loop whose memory plan is frozen, a thread that must
+ * not touch the allocator.  Arguments are those of cwm_paged_attn_fwd with
+ * total_q == batch and max_seqlen_q == 1 (cu_seqlens_q is 0, 1, ..., batch); the
+ * split-KV scratch is a fixed array of about 2.6 MB inside the library image,
+ * which every GPU that loads the library holds until the process exits.
+ *
+ * Limits: batch <= CWM_NOALLOC_MAX_BATCH, otherwise CWM_ERR_WORKSPACE.  The call
+ * performs no cudaMalloc/cudaFree and calls no allocating library routine.  The
+ * first call on each device looks up the address of the array (and, like any
+ * first launch, lets the CUDA runtime load the kernels), so make that first
+ * call before starting a stream capture.  All calls on a device share the one
+ * array: two calls that can overlap on the GPU (different streams without an
+ * ordering between them) race and give wrong results; calls on one stream are
+ * safe.  The array keeps the previous call's contents, which no call relies on. */
+CWM_API int cwm_paged_attn_decode_noalloc(const void* q, const void* k, const void* v, void* out,
+                                          float* lse /* nullable */, const int32_t* cu_seqlens_q,
+                                          const int32_t* seqused_k, const int32_t* block_table,
+                                          int batch, int hq, int hkv, int d, int dtype,
+                                          int page_size, int64_t num_pages,
+                                          int64_t kv_token_stride, int64_t bt_stride,
+                                          int max_seqlen_k, float softmax_scale, int window_left,
+                                          void* stream);
+
 #ifdef __cplusplus
 }
 #endif
