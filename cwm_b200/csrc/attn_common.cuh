@@ -43,8 +43,8 @@ int launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, AttnArgs a, 
                   void* workspace, cudaStream_t stream, int max_ctas = kMaxDecodeCtas);
 // Workspace bytes for a decode grid of at most max_ctas CTAs.
 size_t decode_workspace_bytes_for(int batch, int max_ctas);
-int launch_prefill(const CUtensorMap& kmap, const CUtensorMap& vmap, AttnArgs a, bool bf16,
-                   cudaStream_t stream);
+int launch_prefill_tc(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap,
+                      AttnArgs a, bool bf16, cudaStream_t stream);
 
 // mma.sync m16n8k16 where only rows 0..7 of the accumulator are kept: the two
 // values of rows 8..15 go to scratch registers and enter as zero, so that

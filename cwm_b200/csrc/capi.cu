@@ -90,13 +90,13 @@ struct MapKey {
 // [box_rows x 64 elements] with the 128-byte swizzle.  Maps are cached: FastGen
 // keeps one cache tensor per layer for the life of the engine.
 int get_kv_map(const void* base, long long inner, long long rows, long long stride_bytes,
-               int dtype, int box_rows, CUtensorMap* out) {
+               int dtype, int box_rows, CUtensorMap* out, bool use_cache = true) {
   static std::mutex mu;
   static std::vector<std::pair<MapKey, CUtensorMap>> cache;
   int dev = 0;
   cudaGetDevice(&dev);
   const MapKey key{base, inner, rows, stride_bytes, dtype, box_rows, dev};
-  {
+  if (use_cache) {
     std::lock_guard<std::mutex> lock(mu);
     for (auto& kv : cache) {
       if (kv.first == key) {
@@ -125,7 +125,7 @@ int get_kv_map(const void* base, long long inner, long long rows, long long stri
               "stride %lld B)", static_cast<int>(r), base, inner, rows, stride_bytes);
     return CWM_ERR_CUDA;
   }
-  {
+  if (use_cache) {
     std::lock_guard<std::mutex> lock(mu);
     if (cache.size() >= 1024) cache.erase(cache.begin());
     cache.emplace_back(key, map);
@@ -283,7 +283,12 @@ extern "C" int cwm_paged_attn_fwd(const void* q, const void* k, const void* v, v
     if (rc != CWM_OK) return rc;
   }
   if (max_seqlen_q > 1) {
-    rc = launch_prefill(kmap, vmap, a, bf16, st);
+    // the query tensor changes from call to call: its map is built, not cached
+    CUtensorMap qmap;
+    rc = get_kv_map(q, static_cast<long long>(hq) * d, total_q, static_cast<long long>(hq) * d * 2,
+                    dtype, 128, &qmap, false);
+    if (rc != CWM_OK) return rc;
+    rc = launch_prefill_tc(qmap, kmap, vmap, a, bf16, st);
     if (rc != CWM_OK) return rc;
   }
   return CWM_OK;
