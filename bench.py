@@ -197,7 +197,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="decode_global",
-                    choices=["decode_global", "decode_local", "small", "prefill", "prefill_local"])
+                    choices=["decode_global", "decode_local", "small", "prefill", "prefill_local",
+                             "prefill_small"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -429,16 +430,20 @@ def bench_prefill(args, window_left: int) -> None:
     n0s = torch.randint(0, 16385, (8,), generator=g).tolist()
     peaks, peak_kind = measured_peaks()
     results = []
-    for chunk in range(4):
+    small = args.workload == "prefill_small"  # one short call, for profiler captures
+    for chunk in range(1 if small else 4):
         seq_info = [(n0 + 2048 * chunk, 2048) for n0 in n0s]
+        if small:
+            seq_info = [(3072, 1024)] * 4
         kv_lens = [a + b for a, b in seq_info]
         table, n_pages = make_tables(kv_lens, 1003)
         cache = cwm_b200.RawCache.build_dims(1, HKV, D, n_pages * PAGE, dev, torch.bfloat16)
         cache.caches[0].normal_()
-        bias = cwm_b200.AttnBias.from_seqlens([2048] * 8, kv_lens, table.to(dev), PAGE)
+        bias = cwm_b200.AttnBias.from_seqlens([n1 for _, n1 in seq_info], kv_lens, table.to(dev),
+                                              PAGE)
         q_batch, q_pos = prefill_positions(seq_info, dev)
         freqs = cwm_b200.rope_freqs(D, 1e6).to(dev)
-        t = 8 * 2048
+        t = sum(n1 for _, n1 in seq_info)
         xq = torch.randn(t, HQ, D, device=dev).to(torch.bfloat16)
         xk = torch.randn(t, HKV, D, device=dev).to(torch.bfloat16)
         xv = torch.randn(t, HKV, D, device=dev).to(torch.bfloat16)

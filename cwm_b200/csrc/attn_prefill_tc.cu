@@ -51,6 +51,19 @@ struct QTile {
   int hi;    // last KV tile (hi < lo: nothing visible)
 };
 
+#ifdef CWM_TRACE
+// Development aid: cycle stamps of the first CTA, read back with cwm_trace_read().
+__device__ long long g_trace[4][64][8];
+#define CWM_STAMP(role, iter, slot)                                                   \
+  do {                                                                                \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (iter) < 64) g_trace[role][iter][slot] = clock64(); \
+  } while (0)
+#else
+#define CWM_STAMP(role, iter, slot) \
+  do {                              \
+  } while (0)
+#endif
+
 __device__ __forceinline__ bool visible(int key, int pos, int window_left) {
   return key <= pos && (window_left < 0 || key >= pos - window_left);
 }
@@ -303,16 +316,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (active(x, j)) {
+            CWM_STAMP(2 + x, j, 0);
             if (!mbar_wait_bounded(&bars->p_full[x], pcnt[x] & 1)) {
               ok = false;
               break;
             }
             tc05::fence_after_sync();
+            CWM_STAMP(2 + x, j, 1);
             issue_pv(x, s, pcnt[x] == 0);
+            CWM_STAMP(2 + x, j, 2);
             ++pcnt[x];
             if (lo + j == qt[x].hi) tc05::commit(&bars->o_full[x]);
           }
           if (more && active(x, j + 1)) issue_s(x, s1);
+          CWM_STAMP(2 + x, j, 3);
         }
         if (!ok) break;
         tc05::commit(&bars->v_empty[s]);
@@ -341,40 +358,51 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 
     for (int i = 0; i < nx && ok; ++i) {
       const int k0 = (qt[x].lo + i) * kBN;
+      if (quarter == 0 && lane == 0) CWM_STAMP(x, i, 0);
       if (!mbar_wait_bounded(&bars->s_full[x], i & 1)) {
         ok = false;
         break;
       }
       tc05::fence_after_sync();
+      if (quarter == 0 && lane == 0) CWM_STAMP(x, i, 1);
       const bool full = k0 + kBN - 1 <= wpos_lo && (wl < 0 || k0 >= wpos_hi - wl);
 
-      // ---- pass 1: row maximum of the raw scores
-      uint32_t ra[32], rb[32];
+      // ---- pass 1: row maximum (four loads in flight, one wait; nothing kept)
       float mx = -INFINITY;
-      auto chunk_max = [&](const uint32_t (&v)[32], int kbase) {
-        if (full) {
+      {
+        uint32_t sv[4][32];
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
-        } else {
+        for (int c = 0; c < 4; ++c) tc05::ld32(sv[c], s_addr + c * 32);
+        tc05::wait_ld();
+        if (!full) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            if (visible(kbase + e, pos, wl)) mx = fmaxf(mx, __uint_as_float(v[e]));
+          for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              sv[c][e] = visible(k0 + c * 32 + e, pos, wl) ? sv[c][e] : 0xff800000u;  // -inf
+            }
           }
         }
-      };
-      tc05::ld32(ra, s_addr);
-      tc05::wait_ld();
-      tc05::ld32(rb, s_addr + 32);
-      chunk_max(ra, k0);
-      tc05::wait_ld();
-      tc05::ld32(ra, s_addr + 64);
-      chunk_max(rb, k0 + 32);
-      tc05::wait_ld();
-      tc05::ld32(rb, s_addr + 96);
-      chunk_max(ra, k0 + 64);
-      tc05::wait_ld();
-      chunk_max(rb, k0 + 96);
+        // eight independent chains of three-input maxima
+        float part[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) part[u] = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 16) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              part[u] = max3(part[u], __uint_as_float(sv[c][e + 2 * u]),
+                             __uint_as_float(sv[c][e + 2 * u + 1]));
+            }
+          }
+        }
+        mx = fmaxf(max3(part[0], part[1], part[2]),
+                   max3(max3(part[3], part[4], part[5]), part[6], part[7]));
+      }
 
+      if (quarter == 0 && lane == 0) CWM_STAMP(x, i, 2);
       // ---- running maximum, updated lazily
       const float m_new = fmaxf(m_used, mx * a.scale_log2);
       const bool grow = m_new - m_used > kRescaleThreshold;  // false when both are -inf
@@ -385,48 +413,62 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
           l *= alpha;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            tc05::ld32(ra, o_addr + c * 32);
+            uint32_t ov[32];
+            tc05::ld32(ov, o_addr + c * 32);
             tc05::wait_ld();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) ra[e] = __float_as_uint(__uint_as_float(ra[e]) * alpha);
-            tc05::st32(o_addr + c * 32, ra);
+            for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
+            tc05::st32(o_addr + c * 32, ov);
           }
         }
         m_used = m_new;
       }
       const float mu = m_used == -INFINITY ? 0.f : m_used;
 
+      if (quarter == 0 && lane == 0) CWM_STAMP(x, i, 3);
       // ---- pass 2: P = exp2(S * scale - m), written over S as packed 16-bit pairs
       float psum = 0.f;
-      auto chunk_p = [&](const uint32_t (&v)[32], int kbase, int c) {
-        uint32_t packed[16];
+      {
+        uint32_t sv[4][32];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(v[e]), a.scale_log2, -mu));
-          float p1 = fast_exp2(fmaf(__uint_as_float(v[e + 1]), a.scale_log2, -mu));
-          if (!full) {
-            p0 = visible(kbase + e, pos, wl) ? p0 : 0.f;
-            p1 = visible(kbase + e + 1, pos, wl) ? p1 : 0.f;
+        for (int c = 0; c < 4; ++c) tc05::ld32(sv[c], s_addr + c * 32);
+        tc05::wait_ld();
+        if (quarter == 0 && lane == 0) CWM_STAMP(x, i, 7);
+        if (!full) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              sv[c][e] = visible(k0 + c * 32 + e, pos, wl) ? sv[c][e] : 0xff800000u;  // -inf -> 0
+            }
           }
-          psum += p0 + p1;
-          packed[e >> 1] = pack2<kBf16>(p0, p1);
         }
-        tc05::st16(s_addr + c * 16, packed);
-      };
-      tc05::ld32(ra, s_addr);
-      tc05::wait_ld();
-      tc05::ld32(rb, s_addr + 32);
-      tc05::wait_ld();
-      // chunks 0 and 1 are in registers: their columns may now be overwritten by P
-      chunk_p(ra, k0, 0);
-      tc05::ld32(ra, s_addr + 64);
-      chunk_p(rb, k0 + 32, 1);
-      tc05::wait_ld();
-      tc05::ld32(rb, s_addr + 96);
-      tc05::wait_ld();
-      chunk_p(ra, k0 + 64, 2);
-      chunk_p(rb, k0 + 96, 3);
+        float2 acc[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc[u] = make_float2(0.f, 0.f);
+        const float2 scale2 = make_float2(a.scale_log2, a.scale_log2);
+        const float2 nmu2 = make_float2(-mu, -mu);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float2 t = fma2(make_float2(__uint_as_float(sv[c][e]), __uint_as_float(sv[c][e + 1])),
+                            scale2, nmu2);
+            t.x = fast_exp2(t.x);
+            t.y = fast_exp2(t.y);
+            acc[(e >> 1) & 3] = add2(acc[(e >> 1) & 3], t);
+            packed[e >> 1] = pack2<kBf16>(t.x, t.y);
+          }
+          if (c == 0 && quarter == 0 && lane == 0) CWM_STAMP(x, i, 5);
+          tc05::st16(s_addr + c * 16, packed);
+          if (c == 0 && quarter == 0 && lane == 0) CWM_STAMP(x, i, 6);
+        }
+        const float2 s01 = add2(add2(acc[0], acc[1]), add2(acc[2], acc[3]));
+        psum = s01.x + s01.y;
+      }
       l += psum;
+      if (quarter == 0 && lane == 0) CWM_STAMP(x, i, 4);
       tc05::wait_st();
       tc05::fence_before_sync();
       mbar_arrive(&bars->p_full[x]);
@@ -481,6 +523,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 }
 
 }  // namespace
+
+#ifdef CWM_TRACE
+extern "C" __attribute__((visibility("default"))) int cwm_trace_read(void* host, size_t bytes) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace, bytes));
+}
+#endif
 
 size_t prefill_tc_smem_bytes(int batch) {
   return 2 * kTileBytes + 2 * kStages * kTileBytes + sizeof(Bars) + 2 * sizeof(uint32_t) +
