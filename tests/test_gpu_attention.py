@@ -217,3 +217,34 @@ def test_mha_fwd_rejects_what_is_not_built(ops):
     k4, v4 = d64.kv_views()
     with pytest.raises(ValueError):
         ops.mha_fwd(**{**args, "query": d64.q, "key": k4, "value": v4})
+
+
+# ------------------------------------------------------------ KV-head sharding
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_head_sharded_runs_concatenate_to_the_unsharded_result(ops, world):
+    """What each tensor-parallel rank computes on its own KV heads (local cache rows
+    ``[K_local | V_local]``, local query heads) is the matching slice of the
+    unsharded result.  The prefill kernel treats every (query block, head)
+    independently, so its rows agree bit for bit; the decode kernel divides its
+    tile list differently when the head count changes, so its rows agree within
+    the tolerance of the path."""
+    from cwm_b200.tp import shard_cache_rows, shard_heads
+
+    q_lens = [1, 300, 1, 130]
+    p = make_problem(q_lens, [2000, 300 + 900, 77, 130], seed=41)
+    full, _ = _run(ops, p, 1023)
+    decode_rows = torch.tensor([0, 301])
+    prefill_rows = torch.tensor([r for r in range(sum(q_lens)) if r not in (0, 301)])
+    parts = []
+    for rank in range(world):
+        sh = shard_heads(rank, world, p.hq, p.hkv)
+        local = type(p)(
+            p.q[:, sh.q_begin : sh.q_end].contiguous(), shard_cache_rows(p.cache, sh, p.hkv, p.d),
+            p.cu_seqlens_q, p.seqused_k, p.block_table, p.page_size, sh.n_q, sh.n_kv, p.d,
+        )
+        out, _ = _run(ops, local, 1023)
+        parts.append(out)
+    cat = torch.cat(parts, dim=1)
+    assert torch.equal(cat[prefill_rows].view(torch.int16), full[prefill_rows].view(torch.int16))
+    assert (cat[decode_rows].float() - full[decode_rows].float()).abs().max().item() <= TOL
+    assert _status() == 0
