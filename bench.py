@@ -41,6 +41,11 @@ import torch  # noqa: E402
 HQ, HKV, D, PAGE = 48, 8, 128, 256
 WINDOW_LOCAL = 8191
 L2_BYTES = 126 * 1024 * 1024
+# DRAM bytes moved per algorithmic byte by the decode kernel, from the ncu capture
+# summarised in profiles/decode_kernel_small_ncu_full.txt (536.97 MB read + written
+# for 527.77 MB algorithmic).  The over-fetch is tile granularity at the ends of a
+# context, so it grows in proportion to the work.
+DECODE_TRAFFIC_RATIO = 536.97 / 527.77
 
 
 # ------------------------------------------------------------------ workloads
@@ -402,9 +407,12 @@ def main() -> None:
                         "+ KV-cache write, attention, D2H of the output; the KV cache is "
                         "device-resident state as in the reference engine"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
-                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                     "traffic": int(bytes_rank * DECODE_TRAFFIC_RATIO),
                      "peak_kind": f"of {peak_kind}",
-                     "note": "per GPU; events bracket the decode kernel and its combine kernel"},
+                     "note": "per GPU; events bracket the decode kernel and its combine kernel; "
+                             "traffic is the ncu DRAM read+write of a smaller capture scaled by "
+                             "the algorithmic bytes"},
     }
     if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
         def rows_fn(pages):

@@ -467,12 +467,15 @@ int launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, DecodeArgs a
   }
   int grid = 2 * sm_count();
   if (grid > max_ctas) grid = max_ctas;
-  static bool attr_set[2] = {false, false};
+  // the opt-in to large dynamic shared memory is per device and per kernel
+  static bool attr_set[64][2] = {};
   auto main_k = bf16 ? decode_kernel<true> : decode_kernel<false>;
-  if (!attr_set[bf16 ? 1 : 0]) {
+  int dev = 0;
+  CWM_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !attr_set[dev][bf16 ? 1 : 0]) {
     CWM_CUDA_CHECK(cudaFuncSetAttribute(main_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         110 * 1024));
-    attr_set[bf16 ? 1 : 0] = true;
+    if (dev >= 0 && dev < 64) attr_set[dev][bf16 ? 1 : 0] = true;
   }
   main_k<<<grid, kThreads, smem, stream>>>(kmap, vmap, a);
   CWM_CUDA_CHECK(cudaGetLastError());

@@ -544,7 +544,14 @@ int launch_prefill_tc(const CUtensorMap& qmap, const CUtensorMap& kmap, const CU
     return CWM_ERR_UNSUPPORTED;
   }
   auto k = bf16 ? prefill_tc_kernel<true> : prefill_tc_kernel<false>;
-  CWM_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+  static bool attr_set[64][2] = {};
+  int dev = 0;
+  CWM_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !attr_set[dev][bf16 ? 1 : 0]) {
+    CWM_CUDA_CHECK(
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    if (dev >= 0 && dev < 64) attr_set[dev][bf16 ? 1 : 0] = true;
+  }
   const int pair_heads = a.group % 2 == 0 ? 1 : 0;
   const int unit_rows = pair_heads ? kBM : 2 * kBM;
   // every sequence with t > 1 queries has ceil(t / unit_rows) <= t / unit_rows + 1 units
