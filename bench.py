@@ -203,7 +203,7 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="decode_global",
                     choices=["decode_global", "decode_local", "small", "prefill", "prefill_local",
-                             "prefill_small"])
+                             "prefill_small", "rmsnorm", "rope_kv_write", "mixed", "mixed_local"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -220,6 +220,10 @@ def main() -> None:
     window_left = WINDOW_LOCAL if args.workload.endswith("local") else -1
     if args.workload.startswith("prefill"):
         return bench_prefill(args, window_left)
+    if args.workload in ("rmsnorm", "rope_kv_write"):
+        return bench_helpers(args)
+    if args.workload.startswith("mixed"):
+        return bench_mixed(args, window_left)
 
     if args.workload == "small":
         kv_lens = decode_lengths(32, 2048, 8192, 1002)
@@ -323,26 +327,37 @@ def main() -> None:
             dist.barrier()
             torch.cuda.synchronize()
 
-    for _ in range(max(3, args.warmup)):
+    # The reference engine replays decode from CUDA graphs (generate.py:338-373); so
+    # does the timed region: one captured step, replayed K times.
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
         attn_step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        graph_out = attn_step()
+    for _ in range(max(3, args.warmup)):
+        graph.replay()
     sync_all()
-    start = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    stop = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
         sync_all()
-        for i in range(args.steps):
-            start[i].record()
-            attn_step()
-            stop[i].record()
+        t0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        t1.record()
         sync_all()
+        timed_ms = t0.elapsed_time(t1)
         # keep the sampler alive for at least a few samples on very short runs
-        if sum(s.elapsed_time(e) for s, e in zip(start, stop)) < 500:
+        if timed_ms < 500:
             t_end = time.time() + 0.6
             while time.time() < t_end:
-                attn_step()
+                graph.replay()
             torch.cuda.synchronize()
-    step_ms = [s.elapsed_time(e) for s, e in zip(start, stop)]
-    total_ms = torch.tensor([sum(step_ms)], device=dev)
+    del graph_out
+    total_ms = torch.tensor([timed_ms], device=dev)
     if dist is not None:
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
     total_ms = float(total_ms.item())
@@ -355,7 +370,7 @@ def main() -> None:
     bytes_all = bytes_rank * n_gpus
     value = bytes_all / (ms_per_step * 1e-3) / 1e9
     peaks, peak_kind = measured_peaks()
-    achieved = bytes_rank / (statistics.mean(step_ms) * 1e-3) / 1e9
+    achieved = bytes_rank / (timed_ms / args.steps * 1e-3) / 1e9
 
     # -------------------------------------------------- end to end, host buffers
     h_q = torch.randn(batch, hq_l, D).to(torch.bfloat16).pin_memory()
@@ -397,6 +412,7 @@ def main() -> None:
         "config": {"workload": workload_name, "batch": batch, "heads": f"{HQ}q/{HKV}kv",
                    "heads_per_gpu": f"{hq_l}q/{hkv_l}kv", "head_dim": D, "page_size": PAGE,
                    "window_left": window_left, "kv_bytes_per_gpu": bytes_rank,
+                   "launch": "one captured CUDA-graph step replayed per step",
                    "l2": "inputs larger than L2" if bytes_rank > 2 * L2_BYTES else
                          "inputs not larger than L2 at this sharding", "parallelism": f"tp{n_gpus}"},
         "clocks": clocks.summary(),
@@ -486,6 +502,114 @@ def bench_prefill(args, window_left: int) -> None:
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"],
                      "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"], "traffic": None,
                      "peak_kind": f"of {peak_kind}"},
+    }))
+
+
+def _time_steps(step, steps: int, warmup: int) -> float:
+    """Milliseconds per call of ``step`` (CUDA events around ``steps`` calls)."""
+    for _ in range(max(3, warmup)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def bench_helpers(args) -> None:
+    """HBM-bound helpers at config-4 / config-3 sizes: RMSNorm over [33008, 6144] and
+    the fused rotary + KV-cache write of a 16384-token prefill step."""
+    import cwm_b200
+    from cwm_b200.layer import prefill_positions
+
+    dev = torch.device("cuda", 0)
+    peaks, peak_kind = measured_peaks()
+    if args.workload == "rmsnorm":
+        n, d = 33008, 6144
+        x = torch.randn(n, d, device=dev).to(torch.bfloat16)
+        w = torch.randn(d, device=dev).to(torch.bfloat16)
+        ms = _time_steps(lambda: cwm_b200.rmsnorm(x, w, 1e-5), args.steps, args.warmup)
+        nbytes = 2 * n * d * 2 + d * 2
+        name = "config 4: RMSNorm (eps 1e-5) over [33008, 6144] bf16"
+    else:
+        seq_info = [(4096, 2048)] * 8
+        kv_lens = [a + b for a, b in seq_info]
+        table, n_pages = make_tables(kv_lens, 1003)
+        cache = cwm_b200.RawCache.build_dims(1, HKV, D, n_pages * PAGE, dev, torch.bfloat16)
+        q_batch, q_pos = prefill_positions(seq_info, dev)
+        t = q_pos.shape[0]
+        xq = torch.randn(t, HQ, D, device=dev).to(torch.bfloat16)
+        xk = torch.randn(t, HKV, D, device=dev).to(torch.bfloat16)
+        xv = torch.randn(t, HKV, D, device=dev).to(torch.bfloat16)
+        freqs = cwm_b200.rope_freqs(D, 1e6).to(dev)
+        ck, cv = cache.cache_kv(0)
+        tbl = table.to(dev)
+        ms = _time_steps(
+            lambda: cwm_b200.rope_kv_write(xq, xk, xv, ck, cv, q_pos, freqs, tbl, q_batch, None,
+                                           PAGE),
+            args.steps, args.warmup,
+        )
+        # read q, k, v; write q, k in place; write k, v pages
+        nbytes = t * D * 2 * (2 * HQ + 2 * HKV + HKV + 2 * HKV)
+        name = "config 3: fused rotary + KV-cache write, 8 x 2048 new tokens, 48q/8kv heads"
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": f"{args.workload}_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": name, "bytes": nbytes},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                     "peak_kind": f"of {peak_kind}"},
+    }))
+
+
+def bench_mixed(args, window_left: int) -> None:
+    """Config 4: one varlen call with 16 prefill chunks of 2048 tokens (no cached
+    prefix) and 240 single-token decodes (contexts lognormal, median 6000, sigma 1,
+    clipped to [256, 65536])."""
+    import cwm_b200
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(1004)
+    z = torch.randn(240, generator=g)
+    dec = [int(min(65536, max(256, round(6000 * math.exp(v))))) for v in z.tolist()]
+    q_lens = [2048] * 16 + [1] * 240
+    kv_lens = [2048] * 16 + dec
+    table, n_pages = make_tables(kv_lens, 1004)
+    cache = cwm_b200.RawCache.build_dims(1, HKV, D, n_pages * PAGE, dev, torch.bfloat16)
+    cache.caches[0].normal_()
+    bias = cwm_b200.AttnBias.from_seqlens(q_lens, kv_lens, table.to(dev), PAGE)
+    t = sum(q_lens)
+    xq = torch.randn(t, HQ, D, device=dev).to(torch.bfloat16)
+    ck, cv = cache.cache_kv(0)
+    k4, v4 = ck.reshape(-1, PAGE, HKV, D), cv.reshape(-1, PAGE, HKV, D)
+
+    def step():
+        return cwm_b200.mha_fwd(
+            xq, k4, v4, bias.q_seqinfo.seqstart, None, bias.k_seqinfo.seqlen, None, 2048,
+            bias.k_seqinfo.max_seqlen, 0, bias.block_tables, D**-0.5, True, window_left, -1,
+        )
+
+    ms = _time_steps(step, args.steps, args.warmup)
+    peaks, peak_kind = measured_peaks()
+    dec_bytes = decode_bytes(dec, window_left, HQ, HKV)
+    flops = 4 * D * HQ * prefill_pairs([(0, 2048)] * 16, window_left)
+    bound_ms = dec_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3 + flops / (peaks["bf16_tflops"] * 1e12) * 1e3
+    print(json.dumps({
+        "metric": "mixed_step_ms", "value": ms, "unit": "ms", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": False,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "config 4: 16 prefill chunks of 2048 + 240 decodes in one call",
+                   "window_left": window_left, "decode_kv_bytes": dec_bytes,
+                   "prefill_flops": flops, "sigma": 1.0},
+        "roofline": {"bound": "hbm+tensor", "lower_bound_ms": bound_ms, "frac": bound_ms / ms,
+                     "peak_kind": f"of {peak_kind}",
+                     "note": "lower bound = decode bytes / HBM peak + prefill FLOPs / bf16 peak "
+                             "(the two kernels run back to back on one stream)"},
     }))
 
 
