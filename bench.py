@@ -203,7 +203,11 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="decode_global",
                     choices=["decode_global", "decode_local", "small", "prefill", "prefill_local",
-                             "prefill_small", "rmsnorm", "rope_kv_write", "mixed", "mixed_local"])
+                             "prefill_small", "rmsnorm", "rope_kv_write", "mixed", "mixed_local",
+                             "decoder"])
+    ap.add_argument("--decoder-batch", type=int, default=128)
+    ap.add_argument("--decoder-ctx", type=int, default=16384)
+    ap.add_argument("--decoder-layers", type=int, default=64)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -218,6 +222,8 @@ def main() -> None:
         raise SystemExit("--gpus must divide the 8 KV heads")
 
     window_left = WINDOW_LOCAL if args.workload.endswith("local") else -1
+    if args.workload == "decoder":
+        return bench_decoder(args, rank, local_rank, world)
     if args.workload.startswith("prefill"):
         return bench_prefill(args, window_left)
     if args.workload in ("rmsnorm", "rope_kv_write"):
@@ -503,6 +509,109 @@ def bench_prefill(args, window_left: int) -> None:
                      "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"], "traffic": None,
                      "peak_kind": f"of {peak_kind}"},
     }))
+
+
+def bench_decoder(args, rank: int, local_rank: int, world: int) -> None:
+    """Config 5: whole decode step of a CWM-32B-shaped decoder (random bf16 weights),
+    tensor-parallel over ``world`` GPUs, batch 128, contexts of 16384 tokens whose
+    K/V are random (the prompts are not prefilled: their pages are filled directly),
+    one CUDA-graph replay per step; tokens/s = batch * steps / time.  Sampling is
+    not part of the step."""
+    import cwm_b200
+    from cwm_b200.decoder import DecoderArgs, DecodeState, ShardedDecoder
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    margs = DecoderArgs(n_layers=args.decoder_layers)
+    batch, ctx = args.decoder_batch, args.decoder_ctx
+    total_steps = max(3, args.warmup) + args.steps + 4
+    cols = (ctx + total_steps + PAGE - 1) // PAGE
+    n_pages = batch * cols
+    kv_gb = n_pages * PAGE * (HKV // world) * 2 * D * 2 * margs.n_layers / 1e9
+    free_gb = torch.cuda.mem_get_info(dev)[0] / 1e9
+    if kv_gb + 20 > free_gb:
+        raise SystemExit(f"decoder workload needs {kv_gb:.0f} GB of KV cache per GPU, "
+                         f"{free_gb:.0f} GB free: use more GPUs or smaller --decoder-* values")
+    model = ShardedDecoder(margs, rank, world, dev, seed=5)
+    cache = model.build_cache(n_pages * PAGE)
+    cache.caches[0].normal_()
+    for c in cache.caches[1:]:
+        c.copy_(cache.caches[0])
+    g = torch.Generator().manual_seed(1005)
+    table = torch.randperm(n_pages, generator=g).reshape(batch, cols).to(torch.int32).to(dev)
+    state = DecodeState(batch, table, PAGE, dev)
+    tokens = torch.randint(0, margs.vocab_size, (batch,), generator=g, dtype=torch.int32).to(dev)
+    seqlen = torch.full((batch,), ctx + 1, dtype=torch.int32, device=dev)
+    state.copy_inputs(state.blktbl, tokens, seqlen)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        model.decode(state, cache)
+    torch.cuda.current_stream().wait_stream(side)
+    sync_all()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        logits = model.decode(state, cache)
+
+    def step():
+        graph.replay()
+        state.seqlen.add_(1)  # the next token lands one position further
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        sync_all()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        sync_all()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if dist is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(ms.item()) / args.steps
+    finite = bool(torch.isfinite(logits).all().item())
+    peaks, peak_kind = measured_peaks()
+    lefts = [l["window_left"] for l in model.layers]
+    kv_bytes = sum(attended(ctx + 1, wl) for wl in lefts) * batch * 2 * (HKV // world) * D * 2
+    w_bytes = sum(t.numel() * 2 for l in model.layers for t in l.values() if torch.is_tensor(t))
+    w_bytes += model.output.numel() * 2
+    bound_ms = (kv_bytes + w_bytes) / (peaks["hbm_gbs"] * 1e9) * 1e3
+    line = {
+        "metric": "decode_tokens_per_s", "value": batch / (ms_per_step * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "config 5: CWM-32B-shaped decoder decode step, random weights",
+                   "batch": batch, "context": ctx, "layers": margs.n_layers,
+                   "global_layers": sum(1 for v in lefts if v < 0), "parallelism": f"tp{world}",
+                   "launch": "one CUDA-graph replay per step", "logits_finite": finite,
+                   "sampling": "excluded"},
+        "clocks": clocks.summary(),
+        "roofline": {"bound": "hbm", "lower_bound_ms": bound_ms, "frac": bound_ms / ms_per_step,
+                     "kv_bytes_per_gpu": kv_bytes, "weight_bytes_per_gpu": w_bytes,
+                     "peak_kind": f"of {peak_kind}",
+                     "note": "lower bound = (attended KV + weights read once) / HBM peak; "
+                             "all-reduce time not included"},
+    }
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
 
 
 def _time_steps(step, steps: int, warmup: int) -> float:

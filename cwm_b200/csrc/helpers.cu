@@ -132,22 +132,29 @@ __device__ __forceinline__ uint4 rotate_vec(uint4 raw, const float2* cs) {
   return raw;
 }
 
-// (cos, sin) of the pairs covered by vector `v` of a head, for position `pos`.
+constexpr int kMaxRopePairs = 1024;  // head_dim <= 2048
+
+// Fills tab[i] = (cos, sin)(float(pos) * freqs[i]) for the pairs of one token, the
+// block's threads sharing the work, and loads this thread's pairs (those covered by
+// vector `v` of a head).  The angle and the accurate sine/cosine follow
+// cwm/fastgen/kernels/rope.py:58,74-75.
 template <typename T>
-__device__ __forceinline__ void pair_cos_sin(int pos, int v, const float* __restrict__ freqs,
-                                             float2* cs) {
+__device__ __forceinline__ void token_cos_sin(int pos, int v, int n_pairs,
+                                              const float* __restrict__ freqs, float2* tab,
+                                              float2* cs) {
   constexpr int kP = 8 / sizeof(T);  // pairs per 16-byte vector
   const float fpos = static_cast<float>(pos);
-#pragma unroll
-  for (int i = 0; i < kP; ++i) {
-    const float a = __fmul_rn(fpos, freqs[v * kP + i]);  // rope.py:58
-    cs[i].x = cosf(a);
-    cs[i].y = sinf(a);
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const float a = __fmul_rn(fpos, freqs[i]);
+    tab[i] = make_float2(cosf(a), sinf(a));
   }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < kP; ++i) cs[i] = tab[v * kP + i];
 }
 
 // One block per token.  Thread (hslot, v) owns vector v of heads hslot,
-// hslot + slots, ...; cos/sin are computed once per thread and reused.
+// hslot + slots, ...; cos/sin are computed once per token in shared memory.
 template <typename T>
 __global__ void rope_kernel(uint4* __restrict__ x, const int32_t* __restrict__ pos,
                             const float* __restrict__ freqs, int n_heads, int vecs_per_head) {
@@ -156,9 +163,10 @@ __global__ void rope_kernel(uint4* __restrict__ x, const int32_t* __restrict__ p
   const int v = threadIdx.x % vecs_per_head;
   const int hslot = threadIdx.x / vecs_per_head;
   const int slots = blockDim.x / vecs_per_head;
-  if (hslot >= slots) return;
+  __shared__ float2 tab[kMaxRopePairs];
   float2 cs[kP];
-  pair_cos_sin<T>(pos[n], v, freqs, cs);
+  token_cos_sin<T>(pos[n], v, vecs_per_head * kP, freqs, tab, cs);
+  if (hslot >= slots) return;
   uint4* row = x + n * n_heads * vecs_per_head;
   for (int h = hslot; h < n_heads; h += slots) {
     uint4* p = row + h * vecs_per_head + v;
@@ -184,9 +192,10 @@ __global__ void rope_kv_write_kernel(uint4* __restrict__ xq, uint4* __restrict__
   const int v = threadIdx.x % vecs_per_head;
   const int hslot = threadIdx.x / vecs_per_head;
   const int slots = blockDim.x / vecs_per_head;
-  if (hslot >= slots) return;
+  __shared__ float2 tab[kMaxRopePairs];
   float2 cs[kP];
-  pair_cos_sin<T>(pos[n], v, freqs, cs);
+  token_cos_sin<T>(pos[n], v, vecs_per_head * kP, freqs, tab, cs);
+  if (hslot >= slots) return;
   const long long batch_size = load_batch_size(batch_size_p, batch_size_is_i64);
   const long long row = paged_row(n, page_tbl, pos, src_batch, batch_size, page_size, tbl_stride,
                                   tbl_cols, cache_rows, 0, 1, status);
