@@ -194,6 +194,21 @@ def cpu_decode_baseline(kv_lens, table, cache_rows_fn, window_left, hq, hkv, bud
     }
 
 
+def _finish(dist) -> None:
+    """End of a multi-rank run: wait for every rank, then leave without tearing the
+    communicator down.  Destroying an NCCL communicator whose collectives were
+    captured in a CUDA graph can block for ever, and nothing is left to clean up."""
+    sys.stdout.flush()
+    if dist is None:
+        return
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
 # ------------------------------------------------------------------------ main
 def main() -> None:
     ap = argparse.ArgumentParser()
@@ -445,8 +460,8 @@ def main() -> None:
         )
     if rank == 0:
         print(json.dumps(line))
-    if dist is not None:
-        dist.destroy_process_group()
+    del graph
+    _finish(dist)
 
 
 def bench_prefill(args, window_left: int) -> None:
@@ -610,8 +625,8 @@ def bench_decoder(args, rank: int, local_rank: int, world: int) -> None:
     }
     if rank == 0:
         print(json.dumps(line))
-    if dist is not None:
-        dist.destroy_process_group()
+    del graph, logits
+    _finish(dist)
 
 
 def _time_steps(step, steps: int, warmup: int) -> float:
