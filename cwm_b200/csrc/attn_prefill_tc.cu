@@ -21,6 +21,8 @@
 // overlaps the matrix products of the other.  KV tiles wholly above the causal
 // diagonal or wholly left of the sliding window are never loaded; only edge tiles
 // are masked.  Every mbarrier wait is bounded.  Needs no scratch memory.
+#include <type_traits>
+
 #include "attn_common.cuh"
 #include "tc05.cuh"
 
@@ -35,6 +37,11 @@ constexpr int kTileBytes = 128 * 256;  // [2 halves of 64 elements][128 rows][12
 constexpr int kHalfBytes = 128 * 128;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.f;  // log2 domain
+// Of every four pairs of scores, this many take the polynomial exp2.
+#ifndef CWM_POLY_PAIRS
+#define CWM_POLY_PAIRS 1
+#endif
+constexpr int kPolyPairsOfFour = CWM_POLY_PAIRS;
 
 struct Bars {
   uint64_t q_full;
@@ -448,21 +455,37 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         for (int u = 0; u < 4; ++u) acc[u] = make_float2(0.f, 0.f);
         const float2 scale2 = make_float2(a.scale_log2, a.scale_log2);
         const float2 nmu2 = make_float2(-mu, -mu);
+        // On unmasked tiles a share of the exponentials runs on the FMA pipe to
+        // unload the MUFU.  Masked tiles keep the MUFU for every score: it maps -inf
+        // to an exact zero, which rows without any visible key rely on.
+        auto write_p = [&](auto use_poly) {
+          constexpr bool kPoly = decltype(use_poly)::value;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t packed[16];
+          for (int c = 0; c < 4; ++c) {
+            uint32_t packed[16];
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float2 t = fma2(make_float2(__uint_as_float(sv[c][e]), __uint_as_float(sv[c][e + 1])),
-                            scale2, nmu2);
-            t.x = fast_exp2(t.x);
-            t.y = fast_exp2(t.y);
-            acc[(e >> 1) & 3] = add2(acc[(e >> 1) & 3], t);
-            packed[e >> 1] = pack2<kBf16>(t.x, t.y);
+            for (int e = 0; e < 32; e += 2) {
+              float2 t = fma2(
+                  make_float2(__uint_as_float(sv[c][e]), __uint_as_float(sv[c][e + 1])), scale2,
+                  nmu2);
+              if (kPoly && ((e >> 1) & 3) < kPolyPairsOfFour) {
+                t = poly_exp2_pair(t);
+              } else {
+                t.x = fast_exp2(t.x);
+                t.y = fast_exp2(t.y);
+              }
+              acc[(e >> 1) & 3] = add2(acc[(e >> 1) & 3], t);
+              packed[e >> 1] = pack2<kBf16>(t.x, t.y);
+            }
+            if (c == 0 && quarter == 0 && lane == 0) CWM_STAMP(x, i, 5);
+            tc05::st16(s_addr + c * 16, packed);
+            if (c == 0 && quarter == 0 && lane == 0) CWM_STAMP(x, i, 6);
           }
-          if (c == 0 && quarter == 0 && lane == 0) CWM_STAMP(x, i, 5);
-          tc05::st16(s_addr + c * 16, packed);
-          if (c == 0 && quarter == 0 && lane == 0) CWM_STAMP(x, i, 6);
+        };
+        if (full) {
+          write_p(std::true_type{});
+        } else {
+          write_p(std::false_type{});
         }
         const float2 s01 = add2(add2(acc[0], acc[1]), add2(acc[2], acc[3]));
         psum = s01.x + s01.y;

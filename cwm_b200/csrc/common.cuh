@@ -168,6 +168,27 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
   return r;
 }
 
+// 2^x for a pair of values without the special-function unit: round x to the
+// nearest integer n with the 1.5 * 2^23 trick, evaluate a cubic for 2^(x - n) on
+// [-0.5, 0.5] (relative error 1e-4, below the rounding step of a 16-bit P), and add
+// n to the exponent field.  Valid for x <= 127; values below -126 give ~1e-38.
+__device__ __forceinline__ float2 poly_exp2_pair(float2 x) {
+  const float kMagic = 12582912.f;
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = add2(x, make_float2(kMagic, kMagic));
+  const float2 n = add2(t, make_float2(-kMagic, -kMagic));
+  const float2 f = fma2(n, make_float2(-1.f, -1.f), x);
+  float2 p = fma2(make_float2(0.05583828315138817f, 0.05583828315138817f), f,
+                  make_float2(0.2426394820213318f, 0.2426394820213318f));
+  p = fma2(p, f, make_float2(0.6931367516517639f, 0.6931367516517639f));
+  p = fma2(p, f, make_float2(0.9999245405197144f, 0.9999245405197144f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
+
 template <bool kBf16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if constexpr (kBf16) {
