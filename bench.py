@@ -225,6 +225,9 @@ def main() -> None:
     ap.add_argument("--decoder-layers", type=int, default=64)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--as-shard", type=int, default=1,
+                    help="on one GPU, run the per-GPU share of an N-way KV-head sharding "
+                         "(profiling aid; the line says so)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -313,6 +316,10 @@ def main() -> None:
 
         dist.init_process_group("nccl", device_id=dev)
     hkv_l, hq_l = HKV // n_gpus, HQ // n_gpus
+    if args.as_shard > 1:
+        if n_gpus != 1 or HKV % args.as_shard:
+            raise SystemExit("--as-shard needs --gpus 1 and a divisor of the 8 KV heads")
+        hkv_l, hq_l = HKV // args.as_shard, HQ // args.as_shard
 
     gen = torch.Generator(device=dev).manual_seed(1002 + rank)
     cache = cwm_b200.RawCache.build_dims(1, hkv_l, D, n_pages * PAGE, dev, torch.bfloat16)
@@ -433,6 +440,8 @@ def main() -> None:
         "config": {"workload": workload_name, "batch": batch, "heads": f"{HQ}q/{HKV}kv",
                    "heads_per_gpu": f"{hq_l}q/{hkv_l}kv", "head_dim": D, "page_size": PAGE,
                    "window_left": window_left, "kv_bytes_per_gpu": bytes_rank,
+                   **({"as_shard": f"one GPU running the share of 1 of {args.as_shard} ranks"}
+                      if args.as_shard > 1 else {}),
                    "launch": "one captured CUDA-graph step replayed per step",
                    "l2": "inputs larger than L2" if bytes_rank > 2 * L2_BYTES else
                          "inputs not larger than L2 at this sharding", "parallelism": f"tp{n_gpus}"},

@@ -406,23 +406,35 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
   if (!ok && lane == 0) atomicOr(a.status, DEV_WAIT_TIMEOUT);
 }
 
-// One warp per (KV head, sequence): merge the partials that the persistent CTAs
-// left for this segment, in CTA order, and write the result.  Also writes zeros
-// for decode sequences without any key.
+// One CTA of four warps per (KV head, sequence): merge the partials that the
+// persistent CTAs left for this segment and write the result; also writes zeros for
+// decode sequences without any key.  Warp w owns output columns 32 w .. 32 w + 31 of
+// every head.  Two passes over the partials, both with independent loads (first the
+// maxima, then the weighted sums), always in CTA order, so the result does not
+// depend on timing.
 template <bool kBf16>
-__global__ void decode_combine_kernel(const DecodeArgs a, int grid_main) {
+__global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeArgs a, int grid_main) {
   const int lane = threadIdx.x & 31;
-  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  if (warp_global >= a.batch * a.hkv) return;
-  const int b = warp_global / a.hkv;
-  const int h = warp_global - b * a.hkv;
+  const int warp = threadIdx.x >> 5;
+  const int b = blockIdx.x / a.hkv;
+  const int h = blockIdx.x - b * a.hkv;
   const int q0 = a.cu_q[b];
   if (a.cu_q[b + 1] - q0 != 1) return;
   const int nt = (a.prefix[b + 1] - a.prefix[b]) / a.hkv;
-  Frag f;
-  frag_reset(f);
+  const int g = lane >> 2;
+  const int c = lane & 3;
+  const int head = h * a.group + g;
+  uint32_t* orow = reinterpret_cast<uint32_t*>(a.out) +
+                   (static_cast<long long>(q0) * a.hq + head) * (kHeadDim / 2);
+  float* lse = a.lse != nullptr && warp == 0 && c == 0 && g < a.group
+                   ? a.lse + static_cast<long long>(head) * a.total_q + q0
+                   : nullptr;
   if (nt == 0) {
-    frag_write_out<kBf16>(f, a, q0, h, lane);
+    if (g < a.group) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) orow[(4 * warp + j) * 4 + c] = 0u;
+    }
+    if (lse != nullptr) *lse = -INFINITY;
     return;
   }
   const int total = a.prefix[a.batch];
@@ -432,11 +444,37 @@ __global__ void decode_combine_kernel(const DecodeArgs a, int grid_main) {
   const int c_first = s0 / per;
   const int c_last = (s1 - 1) / per;
   if (c_first == c_last) return;  // written directly by its CTA
-  for (int cta = c_first; cta <= c_last; ++cta) {
+  auto partial_of = [&](int cta) {
     const int slot = s0 <= cta * per ? 0 : 1;
-    frag_merge(f, a.partial + (static_cast<long long>(cta) * 2 + slot) * kPartialFloats, lane);
+    return a.partial + (static_cast<long long>(cta) * 2 + slot) * kPartialFloats;
+  };
+  float m = -INFINITY;
+#pragma unroll 4
+  for (int cta = c_first; cta <= c_last; ++cta) m = fmaxf(m, partial_of(cta)[32 * 32 + lane]);
+  const float mu = m == -INFINITY ? 0.f : m;
+  float l = 0.f;
+  float o[4][2];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) o[j][0] = o[j][1] = 0.f;
+#pragma unroll 4
+  for (int cta = c_first; cta <= c_last; ++cta) {
+    const float* buf = partial_of(cta);
+    const float w = fast_exp2(buf[32 * 32 + lane] - mu);
+    l = fmaf(buf[33 * 32 + lane], w, l);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      o[j][0] = fmaf(buf[(2 * (4 * warp + j)) * 32 + lane], w, o[j][0]);
+      o[j][1] = fmaf(buf[(2 * (4 * warp + j) + 1) * 32 + lane], w, o[j][1]);
+    }
   }
-  frag_write_out<kBf16>(f, a, q0, h, lane);
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  if (g < a.group) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      orow[(4 * warp + j) * 4 + c] = pack2<kBf16>(o[j][0] * inv, o[j][1] * inv);
+    }
+  }
+  if (lse != nullptr) *lse = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
 }
 
 }  // namespace
@@ -479,13 +517,11 @@ int launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, DecodeArgs a
   }
   main_k<<<grid, kThreads, smem, stream>>>(kmap, vmap, a);
   CWM_CUDA_CHECK(cudaGetLastError());
-  const int warps = a.batch * a.hkv;
-  const int cthreads = 128;
-  const int cgrid = (warps * 32 + cthreads - 1) / cthreads;
+  const int cgrid = a.batch * a.hkv;
   if (bf16) {
-    decode_combine_kernel<true><<<cgrid, cthreads, 0, stream>>>(a, grid);
+    decode_combine_kernel<true><<<cgrid, 128, 0, stream>>>(a, grid);
   } else {
-    decode_combine_kernel<false><<<cgrid, cthreads, 0, stream>>>(a, grid);
+    decode_combine_kernel<false><<<cgrid, 128, 0, stream>>>(a, grid);
   }
   CWM_CUDA_CHECK(cudaGetLastError());
   return CWM_OK;
