@@ -248,3 +248,43 @@ def test_head_sharded_runs_concatenate_to_the_unsharded_result(ops, world):
     assert torch.equal(cat[prefill_rows].view(torch.int16), full[prefill_rows].view(torch.int16))
     assert (cat[decode_rows].float() - full[decode_rows].float()).abs().max().item() <= TOL
     assert _status() == 0
+
+
+# ------------------------------------------------- shapes beyond the CWM defaults
+@pytest.mark.parametrize("page_size", [64, 128, 512])
+def test_other_page_sizes(ops, page_size):
+    """Pages smaller than a 128-token prefill tile (two page lookups per tile) and
+    larger than the default."""
+    p = make_problem([1, 200, 1, 300], [700, 200 + 333, 65, 300], hq=12, hkv=2,
+                     page_size=page_size, seed=page_size)
+    _check(ops, p, -1)
+    _check(ops, p, 100)
+
+
+@pytest.mark.parametrize("hq,hkv", [(3, 1), (1, 1), (5, 5), (8, 1), (16, 4)])
+def test_prefill_head_groupings(ops, hq, hkv):
+    """Odd group sizes pair two consecutive 128-row blocks of one head in a CTA, even
+    ones pair two heads; both with ragged lengths around the 128/256-row units."""
+    p = make_problem([2, 128, 129, 256, 257, 500], [2, 128 + 40, 129, 256 + 300, 257, 500 + 77],
+                     hq=hq, hkv=hkv, seed=hq * 7 + hkv)
+    _check(ops, p, -1)
+    _check(ops, p, 190)
+
+
+def test_prefill_fp16(ops):
+    p = make_problem([300, 140], [300 + 500, 140], hq=12, hkv=2, seed=51, dtype=torch.float16)
+    _check(ops, p, -1)
+    _check(ops, p, 255)
+
+
+def test_large_batch_decode_and_prefill(ops):
+    """More sequences than one scan step of the schedulers covers (batch > 32) and more
+    decode segments than persistent CTAs."""
+    g = torch.Generator().manual_seed(61)
+    n = 400
+    kv = torch.randint(1, 400, (n,), generator=g).tolist()
+    q_lens = [1] * n
+    for i in range(0, n, 50):
+        q_lens[i] = min(kv[i], 70)
+    p = make_problem(q_lens, kv, hq=6, hkv=1, seed=61)
+    _check(ops, p, -1)
