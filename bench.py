@@ -553,15 +553,20 @@ def bench_decoder(args, rank: int, local_rank: int, world: int) -> None:
         dist.init_process_group("nccl", device_id=dev)
     margs = DecoderArgs(n_layers=args.decoder_layers)
     batch, ctx = args.decoder_batch, args.decoder_ctx
+    shard_of = world
+    if args.as_shard > 1:
+        if world != 1:
+            raise SystemExit("--as-shard needs a single process")
+        shard_of = args.as_shard
     total_steps = max(3, args.warmup) + args.steps + 4
     cols = (ctx + total_steps + PAGE - 1) // PAGE
     n_pages = batch * cols
-    kv_gb = n_pages * PAGE * (HKV // world) * 2 * D * 2 * margs.n_layers / 1e9
+    kv_gb = n_pages * PAGE * (HKV // shard_of) * 2 * D * 2 * margs.n_layers / 1e9
     free_gb = torch.cuda.mem_get_info(dev)[0] / 1e9
     if kv_gb + 20 > free_gb:
         raise SystemExit(f"decoder workload needs {kv_gb:.0f} GB of KV cache per GPU, "
                          f"{free_gb:.0f} GB free: use more GPUs or smaller --decoder-* values")
-    model = ShardedDecoder(margs, rank, world, dev, seed=5)
+    model = ShardedDecoder(margs, rank, shard_of, dev, seed=5, collectives=shard_of == world)
     cache = model.build_cache(n_pages * PAGE)
     cache.caches[0].normal_()
     for c in cache.caches[1:]:
@@ -611,7 +616,7 @@ def bench_decoder(args, rank: int, local_rank: int, world: int) -> None:
     finite = bool(torch.isfinite(logits).all().item())
     peaks, peak_kind = measured_peaks()
     lefts = [l["window_left"] for l in model.layers]
-    kv_bytes = sum(attended(ctx + 1, wl) for wl in lefts) * batch * 2 * (HKV // world) * D * 2
+    kv_bytes = sum(attended(ctx + 1, wl) for wl in lefts) * batch * 2 * (HKV // shard_of) * D * 2
     w_bytes = sum(t.numel() * 2 for l in model.layers for t in l.values() if torch.is_tensor(t))
     w_bytes += model.output.numel() * 2
     bound_ms = (kv_bytes + w_bytes) / (peaks["hbm_gbs"] * 1e9) * 1e3
@@ -623,6 +628,8 @@ def bench_decoder(args, rank: int, local_rank: int, world: int) -> None:
         "config": {"workload": "config 5: CWM-32B-shaped decoder decode step, random weights",
                    "batch": batch, "context": ctx, "layers": margs.n_layers,
                    "global_layers": sum(1 for v in lefts if v < 0), "parallelism": f"tp{world}",
+                   **({"as_shard": f"one GPU running rank 0 of {shard_of}, no collectives"}
+                      if shard_of != world else {}),
                    "launch": "one CUDA-graph replay per step", "logits_finite": finite,
                    "sampling": "excluded"},
         "clocks": clocks.summary(),

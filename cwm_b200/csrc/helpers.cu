@@ -194,21 +194,49 @@ __global__ void rope_kv_write_kernel(uint4* __restrict__ xq, uint4* __restrict__
   const int slots = blockDim.x / vecs_per_head;
   __shared__ float2 tab[kMaxRopePairs];
   float2 cs[kP];
-  token_cos_sin<T>(pos[n], v, vecs_per_head * kP, freqs, tab, cs);
-  if (hslot >= slots) return;
+  // Loads go out before the sines and cosines are computed, so that their latency
+  // hides behind the arithmetic: up to four query vectors and one K/V vector per
+  // thread are held in registers; further heads (wide models) take the loops below.
+  constexpr int kHeld = 4;
+  uint4* qrow = xq + n * hq * vecs_per_head;
+  uint4* krow = xk + n * hkv * vecs_per_head;
+  const uint4* vrow = xv + n * hkv * vecs_per_head;
+  uint4 qv[kHeld];
+#pragma unroll
+  for (int u = 0; u < kHeld; ++u) {
+    const int h = hslot + u * slots;
+    if (xq != nullptr && h < hq) qv[u] = qrow[h * vecs_per_head + v];
+  }
+  uint4 kv0 = make_uint4(0, 0, 0, 0), vv0 = make_uint4(0, 0, 0, 0);
+  if (hslot < hkv) {
+    kv0 = krow[hslot * vecs_per_head + v];
+    vv0 = vrow[hslot * vecs_per_head + v];
+  }
   const long long batch_size = load_batch_size(batch_size_p, batch_size_is_i64);
   const long long row = paged_row(n, page_tbl, pos, src_batch, batch_size, page_size, tbl_stride,
                                   tbl_cols, cache_rows, 0, 1, status);
+  token_cos_sin<T>(pos[n], v, vecs_per_head * kP, freqs, tab, cs);
   if (xq != nullptr) {
-    uint4* qrow = xq + n * hq * vecs_per_head;
-    for (int h = hslot; h < hq; h += slots) {
+#pragma unroll
+    for (int u = 0; u < kHeld; ++u) {
+      const int h = hslot + u * slots;
+      if (h < hq) qrow[h * vecs_per_head + v] = rotate_vec<T>(qv[u], cs);
+    }
+    for (int h = hslot + kHeld * slots; h < hq; h += slots) {
       uint4* p = qrow + h * vecs_per_head + v;
       *p = rotate_vec<T>(*p, cs);
     }
   }
-  uint4* krow = xk + n * hkv * vecs_per_head;
-  const uint4* vrow = xv + n * hkv * vecs_per_head;
-  for (int h = hslot; h < hkv; h += slots) {
+  if (hslot < hkv) {
+    const int idx = hslot * vecs_per_head + v;
+    const uint4 kr = rotate_vec<T>(kv0, cs);
+    krow[idx] = kr;
+    if (row >= 0) {
+      cache_k[row * cache_stride_vecs + idx] = kr;
+      cache_v[row * cache_stride_vecs + idx] = vv0;
+    }
+  }
+  for (int h = hslot + slots; h < hkv; h += slots) {
     const int idx = h * vecs_per_head + v;
     const uint4 kr = rotate_vec<T>(krow[idx], cs);
     krow[idx] = kr;

@@ -86,14 +86,17 @@ class ShardedDecoder:
 
     def __init__(self, args: DecoderArgs, rank: int, world: int, device: torch.device,
                  dtype: torch.dtype = torch.bfloat16, seed: int = 0, std: float = 0.02,
-                 group: dist.ProcessGroup | None = None) -> None:
+                 group: dist.ProcessGroup | None = None, collectives: bool = True) -> None:
+        """``collectives=False`` builds the shard of ``rank`` without a process group
+        and skips the all-reduces and the logits gather: the per-GPU work of a
+        ``world``-way run on a single GPU, for profiling."""
         if args.ffn_dim % world or args.vocab_size % world:
             raise ValueError("ffn_dim and vocab_size must be divisible by the group size")
         self.args = args
         self.rank, self.world = rank, world
         self.device, self.dtype = device, dtype
         self.shard: HeadShard = shard_heads(rank, world, args.n_heads, args.n_kv_heads)
-        self.coll = Collectives(group) if world > 1 else None
+        self.coll = Collectives(group) if world > 1 and collectives else None
         gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
 
         def w(*shape: int) -> torch.Tensor:
