@@ -155,6 +155,13 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     prefetch_tensormap(&kmap);
     prefetch_tensormap(&vmap);
   }
+  // Launched with programmatic serialization: the CTAs may be resident while the
+  // previous kernel (typically the rotary + cache write, or the combine step of the
+  // previous call, which still reads the workspace) is finishing.  Nothing that
+  // another kernel may have written is read before this returns; the combine kernel
+  // of this call may become resident right away.
+  pdl_wait();
+  pdl_launch_dependents();
   // tiles per sequence -> exclusive prefix over sequences (times KV heads)
   for (int b = tid; b < a.batch; b += kThreads) prefix[b + 1] = seq_info(a, b).ntiles * a.hkv;
   if (tid == 0) prefix[0] = 0;
@@ -418,6 +425,8 @@ __global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeArgs a,
   const int warp = threadIdx.x >> 5;
   const int b = blockIdx.x / a.hkv;
   const int h = blockIdx.x - b * a.hkv;
+  pdl_wait();                // the decode kernel's partials and prefix
+  pdl_launch_dependents();   // the next kernel may become resident meanwhile
   const int q0 = a.cu_q[b];
   if (a.cu_q[b + 1] - q0 != 1) return;
   const int nt = (a.prefix[b + 1] - a.prefix[b]) / a.hkv;
@@ -515,14 +524,10 @@ int launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, DecodeArgs a
                                         110 * 1024));
     if (dev >= 0 && dev < 64) attr_set[dev][bf16 ? 1 : 0] = true;
   }
-  main_k<<<grid, kThreads, smem, stream>>>(kmap, vmap, a);
-  CWM_CUDA_CHECK(cudaGetLastError());
+  CWM_CUDA_CHECK(launch_pdl(main_k, dim3(grid), dim3(kThreads), smem, stream, kmap, vmap, a));
   const int cgrid = a.batch * a.hkv;
-  if (bf16) {
-    decode_combine_kernel<true><<<cgrid, 128, 0, stream>>>(a, grid);
-  } else {
-    decode_combine_kernel<false><<<cgrid, 128, 0, stream>>>(a, grid);
-  }
+  auto combine_k = bf16 ? decode_combine_kernel<true> : decode_combine_kernel<false>;
+  CWM_CUDA_CHECK(launch_pdl(combine_k, dim3(cgrid), dim3(128), 0, stream, a, grid));
   CWM_CUDA_CHECK(cudaGetLastError());
   return CWM_OK;
 }

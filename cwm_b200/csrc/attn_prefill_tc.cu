@@ -109,6 +109,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     prefetch_tensormap(&kmap);
     prefetch_tensormap(&vmap);
   }
+  // Launched with programmatic serialization: resident early, but nothing another
+  // kernel may have written is read before the previous kernel has completed.
+  pdl_wait();
+  pdl_launch_dependents();
   // work units per sequence: 128-row blocks (head pairs) or 256-row double blocks
   const int unit_rows = pair_heads ? kBM : 2 * kBM;
   for (int b = tid; b < a.batch; b += kThreadsTc) {
@@ -587,8 +591,7 @@ int launch_prefill_tc(const CUtensorMap& qmap, const CUtensorMap& kmap, const CU
     return CWM_ERR_UNSUPPORTED;
   }
   dim3 grid(pair_heads ? a.hq / 2 : a.hq, static_cast<unsigned>(max_units), 1);
-  k<<<grid, kThreadsTc, smem, stream>>>(qmap, kmap, vmap, a, pair_heads);
-  CWM_CUDA_CHECK(cudaGetLastError());
+  CWM_CUDA_CHECK(launch_pdl(k, grid, dim3(kThreadsTc), smem, stream, qmap, kmap, vmap, a, pair_heads));
   return CWM_OK;
 }
 

@@ -198,6 +198,7 @@ __global__ void rope_kv_write_kernel(uint4* __restrict__ xq, uint4* __restrict__
   // hides behind the arithmetic: up to four query vectors and one K/V vector per
   // thread are held in registers; further heads (wide models) take the loops below.
   constexpr int kHeld = 4;
+  pdl_launch_dependents();  // the attention kernel may become resident now
   uint4* qrow = xq + n * hq * vecs_per_head;
   uint4* krow = xk + n * hkv * vecs_per_head;
   const uint4* vrow = xv + n * hkv * vecs_per_head;
