@@ -194,6 +194,92 @@ def cpu_decode_baseline(kv_lens, table, cache_rows_fn, window_left, hq, hkv, bud
     }
 
 
+def cpu_prefill_baseline(window_left: int, budget_s: float) -> dict:
+    """Times the oracle on slices of one prefill sequence-chunk of the workload (256
+    queries of a 2048-token chunk on a 6144-token cached prefix, all 48/8 heads) and
+    reports FLOP/s over the unmasked pairs; the whole workload scales by pairs."""
+    from oracle import ref_paged_gqa_attention
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(3)
+    t, n0 = 256, 6144 + 1792  # the last 256 queries of the chunk
+    n = n0 + t
+    npg = (n + PAGE - 1) // PAGE
+    rows = torch.randn(npg * PAGE, HKV * 2 * D, generator=g).to(torch.bfloat16)
+    k, v = torch.split(rows, [HKV * D, HKV * D], dim=1)
+    q = torch.randn(t, HQ, D, generator=g).to(torch.bfloat16)
+    tbl = torch.arange(npg, dtype=torch.int32)[None]
+    spent, reps = 0.0, 0
+    while spent < budget_s:
+        t0 = time.perf_counter()
+        ref_paged_gqa_attention(q, k.reshape(-1, PAGE, HKV, D), v.reshape(-1, PAGE, HKV, D),
+                                torch.tensor([0, t], dtype=torch.int32),
+                                torch.tensor([n], dtype=torch.int32), tbl, D**-0.5, window_left)
+        spent += time.perf_counter() - t0
+        reps += 1
+    flops = 4 * D * HQ * prefill_pairs([(n0, t)], window_left) * reps
+    return {
+        "value": flops / spent / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+        "kind": "port",
+        "sample": f"{reps} passes over 256 queries of one 2048-token chunk on 7936 cached tokens "
+                  f"(48q/8kv heads), fp32 PyTorch restatement, {spent:.1f} s of CPU time; the "
+                  "workload's time is extrapolated by unmasked pairs",
+    }
+
+
+def cpu_decoder_baseline(margs, batch: int, ctx: int, budget_s: float) -> dict:
+    """Times the oracle's decode step for ONE local and ONE global layer of the
+    unsharded model on 2 sequences, and extrapolates to all layers and the whole
+    batch (per-sequence cost times batch: an upper bound on what batching the
+    CPU GEMMs could save is not modelled)."""
+    from oracle.ref_decoder import ref_decode_step
+    from oracle import ref_rope_freqs
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(4)
+    sample = 2
+    hq, hkv, d = margs.n_heads, margs.n_kv_heads, margs.head_dim
+    npg = (ctx + 1 + PAGE - 1) // PAGE
+
+    def layer(window_left):
+        def w(*shape):
+            return torch.randn(*shape, generator=g) * 0.02
+        return {"wq": w(hq * d, margs.dim), "wk": w(hkv * d, margs.dim), "wv": w(hkv * d, margs.dim),
+                "wo": w(margs.dim, hq * d), "w13": w(2 * margs.ffn_dim, margs.dim),
+                "w2": w(margs.dim, margs.ffn_dim), "attention_norm": torch.ones(margs.dim),
+                "ffn_norm": torch.ones(margs.dim), "window_left": window_left}
+
+    weights = {"layers": [layer(-1), layer(margs.local_window - 1)],
+               "tok_embeddings": torch.randn(1024, margs.dim, generator=g) * 0.02,
+               "output": torch.zeros(8, margs.dim), "norm": torch.ones(margs.dim)}
+    caches = [torch.randn(sample * npg * PAGE, hkv * 2 * d, generator=g) for _ in range(2)]
+    tbl = torch.arange(sample * npg, dtype=torch.int32).reshape(sample, npg)
+    tokens = torch.randint(0, 1024, (sample,), generator=g, dtype=torch.int32)
+    seqlen = torch.full((sample,), ctx + 1, dtype=torch.int32)
+    freqs = ref_rope_freqs(d, margs.rope_theta)
+    spent, reps = 0.0, 0
+    while spent < budget_s:
+        t0 = time.perf_counter()
+        ref_decode_step(weights, tokens, seqlen, tbl, caches, freqs, hq, hkv, d, PAGE,
+                        margs.norm_eps)
+        spent += time.perf_counter() - t0
+        reps += 1
+    per_pair = spent / reps  # one global + one local layer, 2 sequences
+    n_global = sum(1 for i in range(margs.n_layers)
+                   if (margs.global_last_layer and i == margs.n_layers - 1)
+                   or i % margs.window_pattern == 0)
+    # a local layer costs at most what the timed pair's average does: scale by layers / 2
+    step_s = per_pair / 2 * margs.n_layers * (batch / sample)
+    return {
+        "value": batch / step_s, "unit": "tokens/s", "cores": torch.get_num_threads(),
+        "kind": "port",
+        "sample": f"{reps} passes of one global + one local layer of the unsharded model on "
+                  f"{sample} sequences of {ctx} tokens, fp32 PyTorch restatement, {spent:.1f} s of "
+                  f"CPU time; extrapolated to {margs.n_layers} layers ({n_global} global) and "
+                  f"{batch} sequences",
+    }
+
+
 def _finish(dist) -> None:
     """End of a multi-rank run: wait for every rank, then leave without tearing the
     communicator down.  Destroying an NCCL communicator whose collectives were
@@ -522,7 +608,11 @@ def bench_prefill(args, window_left: int) -> None:
     total_ms = sum(r[0] for r in results)
     total_flops = sum(r[1] for r in results)
     tf = total_flops / (total_ms * 1e-3) / 1e12
+    extra = {}
+    if not small and not args.no_cpu_baseline:
+        extra["cpu_baseline"] = cpu_prefill_baseline(window_left, args.cpu_seconds)
     print(json.dumps({
+        **extra,
         "metric": "prefill_attn_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": total_ms,
         "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
@@ -640,6 +730,8 @@ def bench_decoder(args, rank: int, local_rank: int, world: int) -> None:
                              "all-reduce time not included"},
     }
     if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:  # single-process runs only
+            line["cpu_baseline"] = cpu_decoder_baseline(margs, batch, ctx, args.cpu_seconds)
         print(json.dumps(line))
     del graph, logits
     _finish(dist)
