@@ -16,7 +16,7 @@ Everything runs through ``libcwm_b200.so``; there is no CPU or Triton fallback.
 from .attention import mha_fwd, rope_kv_write, workspace_for
 from .attn_bias import AttnBias, PagedBlockDiagonalCausalWithOffsetPaddedKeysMask
 from .cache import ModelCache, RawCache
-from .kernels import apply_rope, paged_memcpy, rmsnorm
+from .kernels import add_rmsnorm, apply_rope, paged_memcpy, rmsnorm
 from .layer import gqa_attention, rope_freqs, window_size_left
 
 __all__ = [
@@ -24,6 +24,7 @@ __all__ = [
     "ModelCache",
     "PagedBlockDiagonalCausalWithOffsetPaddedKeysMask",
     "RawCache",
+    "add_rmsnorm",
     "apply_rope",
     "gqa_attention",
     "mha_fwd",

@@ -31,6 +31,10 @@ SIGNATURES: dict[str, tuple] = {
     "cwm_rmsnorm": (
         c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_int, c_void_p],
     ),
+    "cwm_add_rmsnorm": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_int, c_void_p],
+    ),
     "cwm_paged_memcpy": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64,

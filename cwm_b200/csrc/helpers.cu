@@ -251,12 +251,16 @@ __global__ void rope_kv_write_kernel(uint4* __restrict__ xq, uint4* __restrict__
 // --------------------------------------------------------------------- rmsnorm
 // One block per row; the row stays in registers between the sum of squares and
 // the scaling, so HBM sees one read and one write per element.
+// With `delta` the row is first updated in place, x <- round(x + delta) (the
+// residual add of cwm/fastgen/forward.py:769,786, rounded to the storage type like
+// the reference's add_), and the normalisation runs on the rounded sum.
 template <typename T, int kVpt>
-__global__ void rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w,
-                               uint4* __restrict__ out, int row_vecs, float inv_d, float eps) {
+__global__ void rmsnorm_kernel(uint4* __restrict__ x, const uint4* __restrict__ delta,
+                               const uint4* __restrict__ w, uint4* __restrict__ out,
+                               int row_vecs, float inv_d, float eps) {
   constexpr int kE = 16 / sizeof(T);
   const long long n = blockIdx.x;
-  const uint4* xr = x + n * row_vecs;
+  uint4* xr = x + n * row_vecs;
   uint4 regs[kVpt];
   float ss = 0.f;
 #pragma unroll
@@ -264,7 +268,14 @@ __global__ void rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restr
     const int idx = threadIdx.x + i * blockDim.x;
     if (idx < row_vecs) {
       regs[i] = xr[idx];
-      const T* e = reinterpret_cast<const T*>(&regs[i]);
+      T* e = reinterpret_cast<T*>(&regs[i]);
+      if (delta != nullptr) {
+        const uint4 dv = delta[n * row_vecs + idx];
+        const T* de = reinterpret_cast<const T*>(&dv);
+#pragma unroll
+        for (int j = 0; j < kE; ++j) e[j] = from_f32<T>(__fadd_rn(to_f32(e[j]), to_f32(de[j])));
+        xr[idx] = regs[i];
+      }
 #pragma unroll
       for (int j = 0; j < kE; ++j) {
         const float a = to_f32(e[j]);
@@ -336,8 +347,8 @@ __global__ void rmsnorm_generic_kernel(const T* __restrict__ x, const T* __restr
 }
 
 template <typename T>
-int launch_rmsnorm(const void* x, const void* w, void* out, int64_t n, int d, float eps,
-                   cudaStream_t stream) {
+int launch_rmsnorm(const void* x, const void* delta, const void* w, void* out, int64_t n, int d,
+                   float eps, cudaStream_t stream) {
   const float inv_d = 1.0f / static_cast<float>(d);
   const int64_t row_bytes = static_cast<int64_t>(d) * sizeof(T);
   const bool vec_ok = row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
@@ -348,12 +359,13 @@ int launch_rmsnorm(const void* x, const void* w, void* out, int64_t n, int d, fl
   if (vec_ok && row_vecs <= 256 * 8) {
     const int threads = row_vecs >= 512 ? 256 : 128;
     const int vpt = (row_vecs + threads - 1) / threads;
-    auto xs = static_cast<const uint4*>(x);
+    auto xs = static_cast<uint4*>(const_cast<void*>(x));
+    auto ds = static_cast<const uint4*>(delta);
     auto ws = static_cast<const uint4*>(w);
     auto os = static_cast<uint4*>(out);
 #define CWM_RMS_CASE(V)                                                                       \
   case V:                                                                                     \
-    rmsnorm_kernel<T, V><<<grid, threads, 0, stream>>>(xs, ws, os, row_vecs, inv_d, eps);     \
+    rmsnorm_kernel<T, V><<<grid, threads, 0, stream>>>(xs, ds, ws, os, row_vecs, inv_d, eps); \
     break;
     switch (vpt) {
       CWM_RMS_CASE(1)
@@ -370,6 +382,10 @@ int launch_rmsnorm(const void* x, const void* w, void* out, int64_t n, int d, fl
     }
 #undef CWM_RMS_CASE
   } else {
+    if (delta != nullptr) {
+      set_error("add_rmsnorm: rows must be 16-byte aligned multiples of 16 bytes, at most 32 KiB");
+      return CWM_ERR_UNSUPPORTED;
+    }
     rmsnorm_generic_kernel<T><<<grid, 256, 0, stream>>>(
         static_cast<const T*>(x), static_cast<const T*>(w), static_cast<T*>(out), d, inv_d, eps);
   }
@@ -476,13 +492,42 @@ extern "C" int cwm_rmsnorm(const void* x, const void* w, void* out, int64_t n, i
   auto st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case CWM_BF16:
-      return launch_rmsnorm<__nv_bfloat16>(x, w, out, n, d, eps, st);
+      return launch_rmsnorm<__nv_bfloat16>(x, nullptr, w, out, n, d, eps, st);
     case CWM_F16:
-      return launch_rmsnorm<__half>(x, w, out, n, d, eps, st);
+      return launch_rmsnorm<__half>(x, nullptr, w, out, n, d, eps, st);
     case CWM_F32:
-      return launch_rmsnorm<float>(x, w, out, n, d, eps, st);
+      return launch_rmsnorm<float>(x, nullptr, w, out, n, d, eps, st);
     default:
       set_error("rmsnorm: unknown dtype %d", dtype);
+      return CWM_ERR_UNSUPPORTED;
+  }
+}
+
+extern "C" int cwm_add_rmsnorm(void* h, const void* delta, const void* w, void* out, int64_t n,
+                               int d, float eps, int dtype, void* stream) {
+  if (n == 0) return CWM_OK;
+  if (!h || !delta || !w || !out) {
+    set_error("add_rmsnorm: null pointer");
+    return CWM_ERR_INVALID;
+  }
+  if (n < 0 || d <= 0) {
+    set_error("add_rmsnorm: bad size argument");
+    return CWM_ERR_INVALID;
+  }
+  if (reinterpret_cast<uintptr_t>(delta) % 16 != 0) {
+    set_error("add_rmsnorm: delta must be 16-byte aligned");
+    return CWM_ERR_UNSUPPORTED;
+  }
+  auto st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case CWM_BF16:
+      return launch_rmsnorm<__nv_bfloat16>(h, delta, w, out, n, d, eps, st);
+    case CWM_F16:
+      return launch_rmsnorm<__half>(h, delta, w, out, n, d, eps, st);
+    case CWM_F32:
+      return launch_rmsnorm<float>(h, delta, w, out, n, d, eps, st);
+    default:
+      set_error("add_rmsnorm: unknown dtype %d", dtype);
       return CWM_ERR_UNSUPPORTED;
   }
 }

@@ -22,7 +22,7 @@ import torch.nn.functional as F
 
 from .attn_bias import AttnBias
 from .cache import RawCache
-from .kernels import rmsnorm
+from .kernels import add_rmsnorm, rmsnorm
 from .layer import gqa_attention, rope_freqs, window_size_left
 from .tp import Collectives, HeadShard, shard_heads
 
@@ -150,19 +150,23 @@ class ShardedDecoder:
         hq, hkv, d = self.shard.n_q, self.shard.n_kv, a.head_dim
         q_seqpos = state.seqlen - 1  # forward.py:525
         h = self._embed(state.tokens)
+        # every residual add is fused with the normalisation that follows it
+        x = rmsnorm(h, self.layers[0]["attention_norm"], a.norm_eps)
         for i, layer in enumerate(self.layers):
-            x = rmsnorm(h, layer["attention_norm"], a.norm_eps)
             xq = F.linear(x, layer["wq"]).view(-1, hq, d)
             xk = F.linear(x, layer["wk"]).view(-1, hkv, d)
             xv = F.linear(x, layer["wv"]).view(-1, hkv, d)
             attn = gqa_attention(xq, xk, xv, cache, i, state.bias, q_seqpos, None,
                                  state.actual_batch_size, self.freqs, layer["window_left"])
-            h.add_(self._all_reduce(F.linear(attn.flatten(1, 2), layer["wo"])))
-            x = rmsnorm(h, layer["ffn_norm"], a.norm_eps)
+            h_out = self._all_reduce(F.linear(attn.flatten(1, 2), layer["wo"]))
+            x = add_rmsnorm(h, h_out, layer["ffn_norm"], a.norm_eps)
             x13 = F.linear(x, layer["w13"])
             x1, x3 = x13.chunk(2, dim=1)
-            h.add_(self._all_reduce(F.linear(F.silu(x1).mul_(x3), layer["w2"])))
-        h = rmsnorm(h, self.norm, a.norm_eps)
+            h_out = self._all_reduce(F.linear(F.silu(x1).mul_(x3), layer["w2"]))
+            next_norm = (self.layers[i + 1]["attention_norm"] if i + 1 < len(self.layers)
+                         else self.norm)
+            x = add_rmsnorm(h, h_out, next_norm, a.norm_eps)
+        h = x
         logits = F.linear(h, self.output)
         if self.coll is not None:
             gathered = [torch.empty_like(logits) for _ in range(self.world)]

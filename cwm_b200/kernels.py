@@ -69,6 +69,25 @@ def _(x, w, eps):
     return torch.empty_like(x)
 
 
+@torch.library.custom_op("cwm_b200::add_rmsnorm", mutates_args=("h",), device_types="cuda")
+def _add_rmsnorm_op(h: torch.Tensor, delta: torch.Tensor, w: torch.Tensor,
+                    eps: float) -> torch.Tensor:
+    out = torch.empty_like(h)
+    n, d = h.shape
+    with torch.cuda.device(h.device):
+        code = _lib.load().cwm_add_rmsnorm(
+            h.data_ptr(), delta.data_ptr(), w.data_ptr(), out.data_ptr(), n, d, eps,
+            _DTYPES[h.dtype], _stream(h),
+        )
+    _lib.check(code, "add_rmsnorm")
+    return out
+
+
+@_add_rmsnorm_op.register_fake
+def _(h, delta, w, eps):
+    return torch.empty_like(h)
+
+
 @torch.library.custom_op("cwm_b200::paged_memcpy", mutates_args=("dst",), device_types="cuda")
 def _paged_memcpy_op(
     src: torch.Tensor,
@@ -152,6 +171,24 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     _dtype_code(x, "rmsnorm")
     _require_cuda("rmsnorm", x, w)
     return _rmsnorm_op(x, w, float(eps))
+
+
+def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    """``h.add_(delta)`` followed by ``rmsnorm(h, w, eps)`` in one pass over the rows
+    (the residual add and the next normalisation of ``cwm/fastgen/forward.py:769-772``
+    and ``:786-789``).  ``h`` is updated in place, rounded to its dtype exactly as
+    ``add_`` would; the normalised rows are returned as a new tensor."""
+    if h.ndim != 2 or delta.shape != h.shape:
+        raise ValueError("h and delta must be 2-D tensors of the same shape")
+    if not h.is_contiguous() or not delta.is_contiguous():
+        raise ValueError("h and delta must be contiguous")
+    if delta.dtype != h.dtype or w.dtype != h.dtype:
+        raise ValueError("h, delta and w must share a dtype")
+    if tuple(w.shape) != (h.shape[1],) or not w.is_contiguous():
+        raise ValueError(f"w must be a contiguous tensor of shape ({h.shape[1]},)")
+    _dtype_code(h, "add_rmsnorm")
+    _require_cuda("add_rmsnorm", h, delta, w)
+    return _add_rmsnorm_op(h, delta, w, float(eps))
 
 
 def paged_memcpy(

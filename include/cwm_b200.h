@@ -63,6 +63,14 @@ CWM_API int cwm_rope(void* x, const int32_t* pos, const float* freqs, int64_t n,
 CWM_API int cwm_rmsnorm(const void* x, const void* w, void* out, int64_t n, int d, float eps, int dtype,
                 void* stream);
 
+/* Residual add fused with the normalisation that follows it: h[N, D] += delta
+ * (in place, rounded to the storage type) and out = rmsnorm(h, w, eps).  Replaces
+ * the pairs h.add_(h_out); rms_norm(h, w, eps) at cwm/fastgen/forward.py:769-772
+ * and :786-789 (and :571 of the next layer).  Rows must be multiples of 16 bytes,
+ * 16-byte aligned, at most 32 KiB. */
+CWM_API int cwm_add_rmsnorm(void* h, const void* delta, const void* w, void* out, int64_t n, int d,
+                            float eps, int dtype, void* stream);
+
 /* Scatter rows src[N, E] into a paged destination through a block table.
  * Replaces paged_memcpy(...), cwm/fastgen/kernels/paged_memcpy.py:90-228.
  * Row n goes to dst row page_tbl[b, pos / page_size] * page_size + pos % page_size

@@ -109,6 +109,38 @@ def test_rmsnorm_rejects_bad_arguments(ops):
         ops.rmsnorm(x[0], w, 1e-5)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("n,d", [(128, 6144), (1, 6144), (33, 128), (5, 8192)])
+def test_add_rmsnorm_equals_add_then_rmsnorm(ops, dtype, n, d):
+    """The fused residual add + normalisation leaves exactly what ``h.add_(delta)``
+    followed by ``rmsnorm(h, w, eps)`` leaves, in h and in the output."""
+    g = torch.Generator().manual_seed(n * 3 + d)
+    h = torch.randn(n, d, generator=g).to(dtype).to(DEV)
+    delta = torch.randn(n, d, generator=g).to(dtype).to(DEV)
+    w = torch.randn(d, generator=g).to(dtype).to(DEV)
+    h_ref = h.clone()
+    h_ref.add_(delta)
+    want = ops.rmsnorm(h_ref, w, 1e-5)
+    got = ops.add_rmsnorm(h, delta, w, 1e-5)
+    assert torch.equal(h.view(torch.uint8), h_ref.view(torch.uint8))
+    assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
+    exact = ref_rmsnorm(h_ref.cpu(), w.cpu(), 1e-5)
+    rel = ((got.cpu().float() - exact).abs() / exact.abs().clamp_min(1e-2)).max().item()
+    assert rel <= 2 * torch.finfo(dtype).eps + 1e-5
+
+
+def test_add_rmsnorm_rejects_bad_arguments(ops):
+    h = torch.zeros(4, 64, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(64, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        ops.add_rmsnorm(h, h[:2], w, 1e-5)
+    with pytest.raises(ValueError):
+        ops.add_rmsnorm(h, h.float(), w, 1e-5)
+    odd = torch.zeros(4, 100, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):  # rows that are not multiples of 16 bytes are not built
+        ops.add_rmsnorm(odd, odd.clone(), torch.zeros(100, device=DEV, dtype=torch.bfloat16), 1e-5)
+
+
 # ---------------------------------------------------------------- paged_memcpy
 def test_paged_memcpy_golden_bit_exact(ops, golden):
     for name in MEMCPY_CASES:
