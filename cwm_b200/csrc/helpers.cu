@@ -93,12 +93,6 @@ int launch_paged_memcpy(const void* src, void* dst, const int32_t* page_tbl,
 }
 
 // ------------------------------------------------------------------------ rope
-template <typename T>
-struct Vec16 {
-  static constexpr int kElems = 16 / sizeof(T);
-  uint4 raw;
-};
-
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
