@@ -288,3 +288,28 @@ def test_large_batch_decode_and_prefill(ops):
         q_lens[i] = min(kv[i], 70)
     p = make_problem(q_lens, kv, hq=6, hkv=1, seed=61)
     _check(ops, p, -1)
+
+
+def test_randomized_problems(ops):
+    """Seeded random batches: lengths, head groupings, windows, page sizes and the
+    mix of decode and prefill sequences all vary."""
+    g = torch.Generator().manual_seed(20250)
+
+    def rnd(lo, hi):
+        return int(torch.randint(lo, hi + 1, (1,), generator=g))
+
+    for case in range(12):
+        hkv = [1, 2, 4][rnd(0, 2)]
+        group = [1, 2, 3, 6, 8][rnd(0, 4)]
+        page = [64, 128, 256][rnd(0, 2)]
+        batch = rnd(1, 9)
+        q_lens, kv = [], []
+        for _ in range(batch):
+            kind = rnd(0, 2)
+            t = 1 if kind == 0 else rnd(2, 400)
+            n0 = 0 if rnd(0, 3) == 0 else rnd(0, 1500)
+            q_lens.append(t)
+            kv.append(n0 + t if rnd(0, 9) else max(0, t - rnd(0, t)))  # sometimes fewer keys than queries
+        window = [-1, 0, 37, 128, 700, 8191][rnd(0, 5)]
+        p = make_problem(q_lens, kv, hq=hkv * group, hkv=hkv, page_size=page, seed=1000 + case)
+        _check(ops, p, window)

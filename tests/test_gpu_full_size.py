@@ -1,0 +1,152 @@
+"""Parity at the full benchmark sizes, where the CPU oracle cannot cover the whole
+problem: size-independent properties of paged attention (bit-exact invariance under
+a different physical page placement, a window that covers every context equals the
+global layer, splitting a prefill chunk in two calls) plus the CPU oracle on sampled
+sequences / query rows of the full-size problem."""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+from oracle import ref_paged_gqa_attention
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+HQ, HKV, D, PAGE = 48, 8, 128, 256
+
+
+@pytest.fixture(scope="module")
+def ops(lib):
+    import cwm_b200
+
+    return cwm_b200
+
+
+def _tables(kv_lens, gen):
+    pages = [(n + PAGE - 1) // PAGE for n in kv_lens]
+    n_pages = sum(pages)
+    perm = torch.randperm(n_pages, generator=gen)
+    table = torch.zeros(len(kv_lens), max(pages), dtype=torch.int32)
+    ofs = 0
+    for b, npg in enumerate(pages):
+        table[b, :npg] = perm[ofs : ofs + npg].to(torch.int32)
+        ofs += npg
+    return table, n_pages, pages
+
+
+def _attend(ops, q, cache, cu, seqk, table, max_q, window_left):
+    k, v = torch.split(cache, [HKV * D, HKV * D], dim=1)
+    out, _ = ops.mha_fwd(q, k.reshape(-1, PAGE, HKV, D), v.reshape(-1, PAGE, HKV, D), cu, None,
+                         seqk, None, max_q, table.shape[1] * PAGE, 0, table, D**-0.5, True,
+                         window_left, -1)
+    return out
+
+
+def _replace_pages(cache, table, pages, gen):
+    """The same logical contents under a new random physical placement."""
+    n_pages = cache.shape[0] // PAGE
+    new_perm = torch.randperm(n_pages, generator=gen)
+    new_table = torch.zeros_like(table)
+    new_cache = torch.empty_like(cache)
+    src4 = cache.view(n_pages, PAGE, -1)
+    dst4 = new_cache.view(n_pages, PAGE, -1)
+    ofs = 0
+    old_ids, new_ids = [], []
+    for b, npg in enumerate(pages):
+        ids = new_perm[ofs : ofs + npg]
+        new_table[b, :npg] = ids.to(torch.int32)
+        old_ids.append(table[b, :npg].long())
+        new_ids.append(ids)
+        ofs += npg
+    old_ids, new_ids = torch.cat(old_ids).to(cache.device), torch.cat(new_ids).to(cache.device)
+    dst4[new_ids] = src4[old_ids]
+    return new_cache, new_table
+
+
+def test_decode_config2_full_size(ops):
+    """Batch 64, contexts log-uniform in [4096, 32768], 48/8 heads (3.6 GB of KV)."""
+    g = torch.Generator().manual_seed(1002)
+    u = torch.empty(64).uniform_(math.log(4096), math.log(32768), generator=g)
+    kv_lens = [int(round(math.exp(v))) for v in u.tolist()]
+    table, n_pages, pages = _tables(kv_lens, g)
+    gd = torch.Generator(device=DEV).manual_seed(7)
+    cache = torch.empty(n_pages * PAGE, 2 * HKV * D, device=DEV, dtype=torch.bfloat16)
+    for r0 in range(0, cache.shape[0], 1 << 16):
+        blk = cache[r0 : r0 + (1 << 16)]
+        blk.copy_(torch.randn(blk.shape, generator=gd, device=DEV))
+    q = torch.randn(64, HQ, D, generator=gd, device=DEV).to(torch.bfloat16)
+    cu = torch.arange(65, dtype=torch.int32, device=DEV)
+    seqk = torch.tensor(kv_lens, dtype=torch.int32, device=DEV)
+    table_d = table.to(DEV)
+
+    out_global = _attend(ops, q, cache, cu, seqk, table_d, 1, -1)
+    out_local = _attend(ops, q, cache, cu, seqk, table_d, 1, 8191)
+    # a window that covers the longest context is the global layer, bit for bit
+    out_wide = _attend(ops, q, cache, cu, seqk, table_d, 1, 40000)
+    assert torch.equal(out_wide.view(torch.int16), out_global.view(torch.int16))
+    # sequences shorter than the window see the same keys (the split points of the
+    # tile list move with the total work, so the sums may differ in the last bits)
+    short = [b for b, n in enumerate(kv_lens) if n <= 8192]
+    long_ = [b for b, n in enumerate(kv_lens) if n > 12000]
+    assert short and long_
+    assert (out_local[short].float() - out_global[short].float()).abs().max().item() <= 2e-3
+    assert not torch.equal(out_local[long_], out_global[long_])
+    # same contents, different physical pages: identical output, bit for bit
+    new_cache, new_table = _replace_pages(cache, table, pages, g)
+    out_moved = _attend(ops, q, new_cache, cu, seqk, new_table.to(DEV), 1, -1)
+    assert torch.equal(out_moved.view(torch.int16), out_global.view(torch.int16))
+    del new_cache
+    # CPU oracle on three sampled sequences (shortest, longest, one in between)
+    order = sorted(range(64), key=lambda b: kv_lens[b])
+    for b in (order[0], order[31], order[-1]):
+        npg = pages[b]
+        rows = torch.cat([cache[int(pg) * PAGE : (int(pg) + 1) * PAGE] for pg in table[b, :npg]]).cpu()
+        k, v = torch.split(rows, [HKV * D, HKV * D], dim=1)
+        for window_left, got in ((-1, out_global), (8191, out_local)):
+            want, _ = ref_paged_gqa_attention(
+                q[b : b + 1].cpu(), k.reshape(-1, PAGE, HKV, D), v.reshape(-1, PAGE, HKV, D),
+                torch.tensor([0, 1], dtype=torch.int32), torch.tensor([kv_lens[b]], dtype=torch.int32),
+                torch.arange(npg, dtype=torch.int32)[None], D**-0.5, window_left)
+            assert (got[b].cpu().float() - want[0]).abs().max().item() <= 2e-2
+
+
+def test_prefill_config3_full_size_chunk(ops):
+    """One chunk call of config 3: 8 sequences x 2048 new tokens on cached prefixes
+    uniform in [0, 16384]."""
+    g = torch.Generator().manual_seed(1003)
+    n0s = torch.randint(0, 16385, (8,), generator=g).tolist()
+    kv_lens = [n0 + 2048 for n0 in n0s]
+    table, n_pages, pages = _tables(kv_lens, g)
+    gd = torch.Generator(device=DEV).manual_seed(9)
+    cache = torch.randn(n_pages * PAGE, 2 * HKV * D, generator=gd, device=DEV).to(torch.bfloat16)
+    q = torch.randn(8 * 2048, HQ, D, generator=gd, device=DEV).to(torch.bfloat16)
+    cu = torch.arange(0, 8 * 2048 + 1, 2048, dtype=torch.int32, device=DEV)
+    seqk = torch.tensor(kv_lens, dtype=torch.int32, device=DEV)
+    table_d = table.to(DEV)
+    for window_left in (-1, 8191):
+        out = _attend(ops, q, cache, cu, seqk, table_d, 2048, window_left)
+        # the chunk split in two calls of 1024 queries gives the same rows, bit for bit
+        q4 = q.view(8, 2048, HQ, D)
+        cu_half = torch.arange(0, 8 * 1024 + 1, 1024, dtype=torch.int32, device=DEV)
+        first = _attend(ops, q4[:, :1024].reshape(-1, HQ, D).contiguous(), cache, cu_half,
+                        seqk - 1024, table_d, 1024, window_left)
+        second = _attend(ops, q4[:, 1024:].reshape(-1, HQ, D).contiguous(), cache, cu_half, seqk,
+                         table_d, 1024, window_left)
+        o4 = out.view(8, 2048, HQ, D)
+        assert torch.equal(o4[:, :1024].reshape(-1, HQ, D).view(torch.int16), first.view(torch.int16))
+        assert torch.equal(o4[:, 1024:].reshape(-1, HQ, D).view(torch.int16), second.view(torch.int16))
+        # CPU oracle on the last 64 query rows of the sequence with the longest prefix
+        b = max(range(8), key=lambda i: kv_lens[i])
+        npg = pages[b]
+        rows = torch.cat([cache[int(pg) * PAGE : (int(pg) + 1) * PAGE] for pg in table[b, :npg]]).cpu()
+        k, v = torch.split(rows, [HKV * D, HKV * D], dim=1)
+        q_tail = q4[b, -64:].cpu()
+        want, _ = ref_paged_gqa_attention(
+            q_tail, k.reshape(-1, PAGE, HKV, D), v.reshape(-1, PAGE, HKV, D),
+            torch.tensor([0, 64], dtype=torch.int32), torch.tensor([kv_lens[b]], dtype=torch.int32),
+            torch.arange(npg, dtype=torch.int32)[None], D**-0.5, window_left)
+        assert (o4[b, -64:].cpu().float() - want).abs().max().item() <= 2e-2
