@@ -378,10 +378,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
       if (quarter == 0 && lane == 0) CWM_STAMP(x, i, 1);
       const bool full = k0 + kBN - 1 <= wpos_lo && (wl < 0 || k0 >= wpos_hi - wl);
 
-      // ---- pass 1: row maximum (four loads in flight, one wait; nothing kept)
+      // ---- the 128 scores of the row: four loads in flight, one wait, kept in
+      // registers for both the maximum and the exponentials
       float mx = -INFINITY;
+      uint32_t sv[4][32];
       {
-        uint32_t sv[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tc05::ld32(sv[c], s_addr + c * 32);
         tc05::wait_ld();
@@ -422,14 +423,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
           const float mu_new = m_new == -INFINITY ? 0.f : m_new;
           const float alpha = fast_exp2(m_used - mu_new);
           l *= alpha;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t ov[32];
-            tc05::ld32(ov, o_addr + c * 32);
+          // rare (the maximum grew by more than 2^8): small pieces, so that the row
+          // of scores can stay in registers meanwhile
+#pragma unroll 1
+          for (int c = 0; c < 16; ++c) {
+            uint32_t ov[8];
+            tc05::ld8(ov, o_addr + c * 8);
             tc05::wait_ld();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
-            tc05::st32(o_addr + c * 32, ov);
+            for (int e = 0; e < 8; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
+            tc05::st8(o_addr + c * 8, ov);
           }
         }
         m_used = m_new;
@@ -437,23 +440,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
       const float mu = m_used == -INFINITY ? 0.f : m_used;
 
       if (quarter == 0 && lane == 0) CWM_STAMP(x, i, 3);
-      // ---- pass 2: P = exp2(S * scale - m), written over S as packed 16-bit pairs
+      // ---- P = exp2(S * scale - m), written over S as packed 16-bit pairs
       float psum = 0.f;
       {
-        uint32_t sv[4][32];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tc05::ld32(sv[c], s_addr + c * 32);
-        tc05::wait_ld();
-        if (quarter == 0 && lane == 0) CWM_STAMP(x, i, 7);
-        if (!full) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              sv[c][e] = visible(k0 + c * 32 + e, pos, wl) ? sv[c][e] : 0xff800000u;  // -inf -> 0
-            }
-          }
-        }
         float2 acc[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) acc[u] = make_float2(0.f, 0.f);
