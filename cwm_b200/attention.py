@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from .kernels import _DTYPES, _ptr, _require_cuda, _stream
+from .kernels import _DTYPES, _ptr, _require_cuda, _stream, _use_registered_op
 
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 # batch size the cached workspace is sized for; larger batches get a fresh one
@@ -41,8 +41,7 @@ def workspace_for(device: torch.device, batch: int) -> torch.Tensor:
     return ws
 
 
-@torch.library.custom_op("cwm_b200::paged_attn_fwd", mutates_args=(), device_types="cuda")
-def _paged_attn_op(
+def _paged_attn_impl(
     query: torch.Tensor,
     key: torch.Tensor,
     value: torch.Tensor,
@@ -72,6 +71,10 @@ def _paged_attn_op(
         )
     _lib.check(code, "mha_fwd")
     return out, lse
+
+
+_paged_attn_op = torch.library.custom_op(
+    "cwm_b200::paged_attn_fwd", mutates_args=(), device_types="cuda")(_paged_attn_impl)
 
 
 @_paged_attn_op.register_fake
@@ -166,17 +169,13 @@ def mha_fwd(
     _require_cuda("mha_fwd", query, key, value, cu_seqlens_q, seqused_k, block_table)
     # never read past the block table, whatever bound the caller gave
     max_k = min(int(max_seqlen_k), block_table.shape[1] * page_size)
-    return _paged_attn_op(
+    return (_paged_attn_op if _use_registered_op() else _paged_attn_impl)(
         query, key, value, cu_seqlens_q, seqused_k, block_table, int(max_seqlen_q), max_k,
         float(softmax_scale), int(window_left),
     )
 
 
-@torch.library.custom_op(
-    "cwm_b200::rope_kv_write", mutates_args=("xq", "xk", "cache_k", "cache_v"),
-    device_types="cuda",
-)
-def _rope_kv_write_op(
+def _rope_kv_write_impl(
     xq: torch.Tensor,
     xk: torch.Tensor,
     xv: torch.Tensor,
@@ -200,6 +199,11 @@ def _rope_kv_write_op(
             cache_k.stride(0), cache_k.shape[0], _stream(xq),
         )
     _lib.check(code, "rope_kv_write")
+
+
+_rope_kv_write_op = torch.library.custom_op(
+    "cwm_b200::rope_kv_write", mutates_args=("xq", "xk", "cache_k", "cache_v"),
+    device_types="cuda")(_rope_kv_write_impl)
 
 
 def rope_kv_write(
@@ -267,5 +271,5 @@ def rope_kv_write(
             raise ValueError("src_batch and batch_size cannot be given together")
     _require_cuda("rope_kv_write", xq, xk, xv, cache_k, cache_v, pos, freqs, page_tbl,
                   src_batch, batch_size)
-    _rope_kv_write_op(xq, xk, xv, cache_k, cache_v, pos, freqs, page_tbl, src_batch, batch_size,
-                      page_size)
+    fn = _rope_kv_write_op if _use_registered_op() else _rope_kv_write_impl
+    fn(xq, xk, xv, cache_k, cache_v, pos, freqs, page_tbl, src_batch, batch_size, page_size)

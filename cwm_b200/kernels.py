@@ -42,8 +42,17 @@ def _require_cuda(what: str, *tensors: torch.Tensor | None) -> None:
 
 
 # ----------------------------------------------------------------- custom ops
-@torch.library.custom_op("cwm_b200::rope", mutates_args=("x",), device_types="cuda")
-def _rope_op(x: torch.Tensor, pos: torch.Tensor, freqs: torch.Tensor) -> None:
+# Each op exists twice: as a plain function that calls the C ABI, and registered as
+# ``torch.ops.cwm_b200.*`` (schema, mutation annotations, fake implementation) for
+# code that is traced or compiled.  In eager mode, CUDA-graph capture included, the
+# public wrappers call the plain function: the dispatcher adds tens of microseconds
+# per call and nothing that eager execution needs.
+def _use_registered_op() -> bool:
+    return torch.compiler.is_compiling()
+
+
+
+def _rope_impl(x: torch.Tensor, pos: torch.Tensor, freqs: torch.Tensor) -> None:
     n, h, d = x.shape
     with torch.cuda.device(x.device):
         code = _lib.load().cwm_rope(
@@ -52,8 +61,11 @@ def _rope_op(x: torch.Tensor, pos: torch.Tensor, freqs: torch.Tensor) -> None:
     _lib.check(code, "apply_rope")
 
 
-@torch.library.custom_op("cwm_b200::rmsnorm", mutates_args=(), device_types="cuda")
-def _rmsnorm_op(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+_rope_op = torch.library.custom_op(
+    "cwm_b200::rope", mutates_args=("x",), device_types="cuda")(_rope_impl)
+
+
+def _rmsnorm_impl(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     out = torch.empty_like(x)
     n, d = x.shape
     with torch.cuda.device(x.device):
@@ -64,13 +76,16 @@ def _rmsnorm_op(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return out
 
 
+_rmsnorm_op = torch.library.custom_op(
+    "cwm_b200::rmsnorm", mutates_args=(), device_types="cuda")(_rmsnorm_impl)
+
+
 @_rmsnorm_op.register_fake
 def _(x, w, eps):
     return torch.empty_like(x)
 
 
-@torch.library.custom_op("cwm_b200::add_rmsnorm", mutates_args=("h",), device_types="cuda")
-def _add_rmsnorm_op(h: torch.Tensor, delta: torch.Tensor, w: torch.Tensor,
+def _add_rmsnorm_impl(h: torch.Tensor, delta: torch.Tensor, w: torch.Tensor,
                     eps: float) -> torch.Tensor:
     out = torch.empty_like(h)
     n, d = h.shape
@@ -83,13 +98,16 @@ def _add_rmsnorm_op(h: torch.Tensor, delta: torch.Tensor, w: torch.Tensor,
     return out
 
 
+_add_rmsnorm_op = torch.library.custom_op(
+    "cwm_b200::add_rmsnorm", mutates_args=("h",), device_types="cuda")(_add_rmsnorm_impl)
+
+
 @_add_rmsnorm_op.register_fake
 def _(h, delta, w, eps):
     return torch.empty_like(h)
 
 
-@torch.library.custom_op("cwm_b200::paged_memcpy", mutates_args=("dst",), device_types="cuda")
-def _paged_memcpy_op(
+def _paged_memcpy_impl(
     src: torch.Tensor,
     dst: torch.Tensor,
     page_tbl: torch.Tensor,
@@ -110,6 +128,10 @@ def _paged_memcpy_op(
             dst.stride(0), dst.shape[0], shard_idx, shard_cnt, _stream(src),
         )
     _lib.check(code, "paged_memcpy")
+
+
+_paged_memcpy_op = torch.library.custom_op(
+    "cwm_b200::paged_memcpy", mutates_args=("dst",), device_types="cuda")(_paged_memcpy_impl)
 
 
 # ------------------------------------------------------------ public wrappers
@@ -146,7 +168,7 @@ def apply_rope(
         raise ValueError(f"freqs must be a float32 tensor, got {freqs.dtype}")
     _dtype_code(x, "apply_rope")
     _require_cuda("apply_rope", x, pos, freqs)
-    _rope_op(x, pos, freqs)
+    (_rope_op if _use_registered_op() else _rope_impl)(x, pos, freqs)
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
@@ -170,7 +192,7 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
         raise ValueError(f"w must have the dtype of x ({x.dtype}), got {w.dtype}")
     _dtype_code(x, "rmsnorm")
     _require_cuda("rmsnorm", x, w)
-    return _rmsnorm_op(x, w, float(eps))
+    return (_rmsnorm_op if _use_registered_op() else _rmsnorm_impl)(x, w, float(eps))
 
 
 def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
@@ -188,7 +210,8 @@ def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, eps: floa
         raise ValueError(f"w must be a contiguous tensor of shape ({h.shape[1]},)")
     _dtype_code(h, "add_rmsnorm")
     _require_cuda("add_rmsnorm", h, delta, w)
-    return _add_rmsnorm_op(h, delta, w, float(eps))
+    fn = _add_rmsnorm_op if _use_registered_op() else _add_rmsnorm_impl
+    return fn(h, delta, w, float(eps))
 
 
 def paged_memcpy(
@@ -259,4 +282,5 @@ def paged_memcpy(
     if page_size <= 0:
         raise ValueError(f"page_size must be positive, got {page_size}")
     _require_cuda("paged_memcpy", src, dst, page_tbl, dst_pos, src_batch, batch_size)
-    _paged_memcpy_op(src, dst, page_tbl, dst_pos, k, s, src_batch, batch_size, page_size)
+    fn = _paged_memcpy_op if _use_registered_op() else _paged_memcpy_impl
+    fn(src, dst, page_tbl, dst_pos, k, s, src_batch, batch_size, page_size)

@@ -131,3 +131,32 @@ def test_decode_layer_replayed_from_a_cuda_graph(ops):
         assert got[nactive:].abs().sum().item() == 0
         _cache_checks(cache.caches[0], ref_cache)
         ref_cache.copy_(cache.caches[0].cpu())
+
+
+def test_registered_torch_ops_match_the_eager_wrappers(ops):
+    """The ops are also registered as ``torch.ops.cwm_b200.*`` for traced or compiled
+    code; called through the dispatcher they give the same bits as the wrappers."""
+    from tests.helpers import make_problem
+
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(9, 6144, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(6144, generator=g).to(torch.bfloat16).to(DEV)
+    assert torch.equal(torch.ops.cwm_b200.rmsnorm(x, w, 1e-5), ops.rmsnorm(x, w, 1e-5))
+    h1, h2 = x.clone(), x.clone()
+    d = torch.randn(9, 6144, generator=g).to(torch.bfloat16).to(DEV)
+    assert torch.equal(torch.ops.cwm_b200.add_rmsnorm(h1, d, w, 1e-5), ops.add_rmsnorm(h2, d, w, 1e-5))
+    assert torch.equal(h1, h2)
+    r1 = torch.randn(7, 6, 128, generator=g).to(torch.bfloat16).to(DEV)
+    r2 = r1.clone()
+    pos = torch.arange(7, dtype=torch.int32, device=DEV)
+    freqs = ref_rope_freqs(128, 1e6).to(DEV)
+    torch.ops.cwm_b200.rope(r1, pos, freqs)
+    ops.apply_rope(r2, pos, freqs)
+    assert torch.equal(r1, r2)
+    p = make_problem([1, 150], [500, 150 + 60], hq=12, hkv=2, seed=77).to(DEV)
+    k4, v4 = p.kv_views()
+    out_op, lse_op = torch.ops.cwm_b200.paged_attn_fwd(
+        p.q, k4, v4, p.cu_seqlens_q, p.seqused_k, p.block_table, 150, 512, 128**-0.5, -1)
+    out, lse = ops.mha_fwd(p.q, k4, v4, p.cu_seqlens_q, None, p.seqused_k, None, 150, 512, 0,
+                           p.block_table, 128**-0.5, True, -1, -1)
+    assert torch.equal(out_op, out) and torch.equal(lse_op, lse)
