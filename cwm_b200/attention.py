@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from .kernels import _DTYPES, _ptr, _require_cuda, _stream, _use_registered_op
+from .kernels import _DTYPES, _on_device, _ptr, _require_cuda, _stream, _use_registered_op
 
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 # batch size the cached workspace is sized for; larger batches get a fresh one
@@ -27,14 +27,15 @@ def workspace_for(device: torch.device, batch: int) -> torch.Tensor:
     graph is being captured a fresh buffer is taken from the graph's pool instead,
     so that the captured kernels never point at memory the cache could drop.
     """
-    lib = _lib.load()
     if torch.cuda.is_current_stream_capturing():
-        need = lib.cwm_paged_attn_workspace_bytes(batch, 0, 0, 0, 0)
+        need = _lib.load().cwm_paged_attn_workspace_bytes(batch, 0, 0, 0, 0)
         return torch.empty(need, dtype=torch.uint8, device=device)
     key = (device.index if device.index is not None else torch.cuda.current_device(),
            torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
-    need = lib.cwm_paged_attn_workspace_bytes(max(batch, _WS_BATCH), 0, 0, 0, 0)
+    if ws is not None and batch <= _WS_BATCH:
+        return ws
+    need = _lib.load().cwm_paged_attn_workspace_bytes(max(batch, _WS_BATCH), 0, 0, 0, 0)
     if ws is None or ws.numel() < need:
         ws = torch.empty(need, dtype=torch.uint8, device=device)
         _workspaces[key] = ws
@@ -61,7 +62,7 @@ def _paged_attn_impl(
     if total_q == 0 or batch == 0:
         return out, lse
     ws = workspace_for(query.device, batch)
-    with torch.cuda.device(query.device):
+    with _on_device(query):
         code = _lib.load().cwm_paged_attn_fwd(
             query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(), lse.data_ptr(),
             cu_seqlens_q.data_ptr(), seqused_k.data_ptr(), block_table.data_ptr(), batch,
@@ -190,7 +191,7 @@ def _rope_kv_write_impl(
 ) -> None:
     t, hq, d = xq.shape
     hkv = xk.shape[1]
-    with torch.cuda.device(xq.device):
+    with _on_device(xq):
         code = _lib.load().cwm_rope_kv_write(
             xq.data_ptr(), xk.data_ptr(), xv.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(),
             pos.data_ptr(), freqs.data_ptr(), page_tbl.data_ptr(), _ptr(src_batch),

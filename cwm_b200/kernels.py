@@ -22,6 +22,25 @@ def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+class _NoSwitch:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def _on_device(t: torch.Tensor):
+    """Context that makes ``t``'s device current for the C-ABI call; free when it
+    already is (the usual one-process-per-GPU case)."""
+    if t.device.index is None or t.device.index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(t.device)
+
+
 def _dtype_code(t: torch.Tensor, what: str) -> int:
     try:
         return _DTYPES[t.dtype]
@@ -54,7 +73,7 @@ def _use_registered_op() -> bool:
 
 def _rope_impl(x: torch.Tensor, pos: torch.Tensor, freqs: torch.Tensor) -> None:
     n, h, d = x.shape
-    with torch.cuda.device(x.device):
+    with _on_device(x):
         code = _lib.load().cwm_rope(
             x.data_ptr(), pos.data_ptr(), freqs.data_ptr(), n, h, d, _DTYPES[x.dtype], _stream(x)
         )
@@ -68,7 +87,7 @@ _rope_op = torch.library.custom_op(
 def _rmsnorm_impl(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     out = torch.empty_like(x)
     n, d = x.shape
-    with torch.cuda.device(x.device):
+    with _on_device(x):
         code = _lib.load().cwm_rmsnorm(
             x.data_ptr(), w.data_ptr(), out.data_ptr(), n, d, eps, _DTYPES[x.dtype], _stream(x)
         )
@@ -89,7 +108,7 @@ def _add_rmsnorm_impl(h: torch.Tensor, delta: torch.Tensor, w: torch.Tensor,
                     eps: float) -> torch.Tensor:
     out = torch.empty_like(h)
     n, d = h.shape
-    with torch.cuda.device(h.device):
+    with _on_device(h):
         code = _lib.load().cwm_add_rmsnorm(
             h.data_ptr(), delta.data_ptr(), w.data_ptr(), out.data_ptr(), n, d, eps,
             _DTYPES[h.dtype], _stream(h),
@@ -119,7 +138,7 @@ def _paged_memcpy_impl(
     page_size: int,
 ) -> None:
     n, e = src.shape
-    with torch.cuda.device(src.device):
+    with _on_device(src):
         code = _lib.load().cwm_paged_memcpy(
             src.data_ptr(), dst.data_ptr(), page_tbl.data_ptr(), dst_pos.data_ptr(),
             _ptr(src_batch), _ptr(batch_size),
