@@ -306,18 +306,22 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     }
   };
 
+  // A wait that runs out (or a producer that gave up) must not strand the other
+  // warps at the named barriers of flush(): the warp stops waiting and computing but
+  // keeps walking its tile list, so every warp passes the same barriers and the CTA
+  // ends; the status word tells the host that the output is not valid.
   bool ok = true;
   int it = 0;
   for (int gi = g_begin; gi < g_end; ++gi, ++it) {
     const int s = it % kStages;
     const uint32_t ph = (it / kStages) & 1;
-    if (!mbar_wait_bounded(&full_bar[s], ph) || *((volatile int*)&abort_flag)) {
+    if (ok && (!mbar_wait_bounded(&full_bar[s], ph) || *((volatile int*)&abort_flag))) {
       ok = false;
-      break;
+      abort_flag = 1;
     }
     const uint32_t st = smem_u32(stages + s * kStageBytes);
     const int tok0 = (si.tile0 + t) * kTile + warp * 16;
-    if (tok0 + 16 > si.lo && tok0 < si.ctx) {
+    if (ok && tok0 + 16 > si.lo && tok0 < si.ctx) {
       // ---- S = Q K^T for 16 tokens: two n-tiles of 8 tokens
       float sacc[2][4];
 #pragma unroll
@@ -409,7 +413,7 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
       if (gi + 1 < g_end) load_q();
     }
   }
-  if (ok && t > 0) flush(seg_start + si.ntiles);
+  if (t > 0) flush(seg_start + si.ntiles);
   if (!ok && lane == 0) atomicOr(a.status, DEV_WAIT_TIMEOUT);
 }
 
