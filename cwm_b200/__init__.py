@@ -17,7 +17,7 @@ from .attention import mha_fwd, rope_kv_write, workspace_for
 from .attn_bias import AttnBias, PagedBlockDiagonalCausalWithOffsetPaddedKeysMask
 from .cache import ModelCache, RawCache
 from .kernels import add_rmsnorm, apply_rope, paged_memcpy, rmsnorm
-from .layer import gqa_attention, rope_freqs, window_size_left
+from .layer import gqa_attention, prefill_chunks, rope_freqs, window_size_left
 
 __all__ = [
     "AttnBias",
@@ -29,6 +29,7 @@ __all__ = [
     "gqa_attention",
     "mha_fwd",
     "paged_memcpy",
+    "prefill_chunks",
     "rmsnorm",
     "rope_freqs",
     "rope_kv_write",

@@ -71,6 +71,52 @@ def prefill_positions(
     )
 
 
+def prefill_chunks(
+    seq_info: list[tuple[int, int]], max_prefill: int
+) -> list[tuple[int, int, int, list[tuple[int, int]]]]:
+    """Cuts a prefill batch into calls of at most ``max_prefill`` new tokens, the way
+    the reference engine does (``cwm/fastgen/generate.py:880-944``).
+
+    ``seq_info`` holds ``(cached, new)`` token counts per lane, in the order in which
+    the new tokens are concatenated.  Returns one entry per call:
+    ``(first_token, last_token, first_lane, lane_seq_info)`` — the half-open range of
+    the concatenated tokens to feed, the index of the first lane of the call, and the
+    ``(cached, new)`` pairs of its lanes (a lane cut by the previous call continues
+    with its cached count advanced).  As in the reference, a cut that would fall
+    exactly on the end of a lane is moved one token back, so that every lane's last
+    token is part of the call that also starts the next lane or ends the batch (its
+    logits are the ones that are kept); a lane can therefore appear in a call with zero
+    new tokens, which the attention ops treat as an empty sequence.
+    """
+    if max_prefill < 2:
+        raise ValueError("max_prefill must be at least 2")
+    info = [(int(c), int(n)) for c, n in seq_info]
+    starts, total = [], 0
+    for _, n in info:
+        if n <= 0:
+            raise ValueError("every lane needs at least one new token")
+        starts.append(total)
+        total += n
+    calls = []
+    first_tok, last_tok, first_lane = 0, max_prefill, 0
+    while last_tok < total:
+        # the lane that contains token last_tok - 1 ... the cut lies inside it or at its end
+        lane = max(i for i in range(first_lane, len(info)) if starts[i] < last_tok)
+        cached, n = info[lane]
+        taken = last_tok - starts[lane]
+        if taken == n:
+            taken -= 1
+            last_tok -= 1
+        lanes = info[first_lane:lane] + [(cached, taken)]
+        calls.append((first_tok, last_tok, first_lane, lanes))
+        info[lane] = (cached + taken, n - taken)
+        starts[lane] += taken
+        first_lane, first_tok = lane, last_tok
+        last_tok += max_prefill
+    calls.append((first_tok, total, first_lane, info[first_lane:]))
+    return calls
+
+
 def gqa_attention(
     xq: torch.Tensor,
     xk: torch.Tensor,

@@ -25,6 +25,7 @@ from .ref_ops import (  # noqa: F401
     ref_gqa_attention_layer,
     ref_paged_gqa_attention,
     ref_paged_memcpy,
+    ref_prefill_splits,
     ref_rmsnorm,
     ref_rope,
     ref_rope_freqs,

@@ -216,3 +216,38 @@ def ref_gqa_attention_layer(
         window_left,
     )
     return out
+
+
+def ref_prefill_splits(seq_info: list[tuple[int, int]], max_prefill: int):
+    """The prefill splitting loop of ``cwm/fastgen/generate.py:880-944`` with the model
+    calls replaced by a record of their arguments: returns, per call, the token range
+    ``(fst_tok, lst_tok)``, the first lane index and the ``seq_info`` slice passed to
+    ``fwd.prefill``.  Log-probability handling (``:913-917``) is left out."""
+    import bisect
+
+    seq_info = list(seq_info)
+    start_pos, total = [], 0
+    for _, n in seq_info:
+        start_pos.append(total)
+        total += n
+    calls = []
+    fst_tok, lst_tok, fst_idx = 0, max_prefill, 0
+    while lst_tok < total:
+        lst_idx = bisect.bisect_left(start_pos, lst_tok, fst_idx)
+        split_idx = lst_idx - 1
+        cached, ntoks = seq_info[split_idx]
+        new_ntoks = lst_tok - start_pos[split_idx]
+        if new_ntoks == ntoks:
+            new_ntoks -= 1
+            lst_tok -= 1
+        seq_info[split_idx] = (cached, new_ntoks)
+        calls.append((fst_tok, lst_tok, fst_idx, list(seq_info[fst_idx:lst_idx])))
+        cached += new_ntoks
+        ntoks -= new_ntoks
+        seq_info[split_idx] = (cached, ntoks)
+        start_pos[split_idx] += new_ntoks
+        fst_idx = split_idx
+        fst_tok = lst_tok
+        lst_tok += max_prefill
+    calls.append((fst_tok, total, fst_idx, list(seq_info[fst_idx:])))
+    return calls

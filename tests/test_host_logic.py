@@ -149,3 +149,41 @@ def test_head_sharding_arithmetic():
     local = shard_cache_rows(rows, shard_heads(1, 4, 48, 8), 8, 4)
     assert local.shape == (4, 2 * 2 * 4)
     assert torch.equal(local[:, :8], rows[:, 8:16]) and torch.equal(local[:, 8:], rows[:, 40:48])
+
+
+def test_prefill_chunks_match_the_reference_loop():
+    """Chunk splitting for prompts longer than the prefill budget, against a literal
+    restatement of the reference's loop, plus its invariants."""
+    import random
+
+    from oracle import ref_prefill_splits
+
+    rng = random.Random(3)
+    for _ in range(300):
+        lanes = rng.randint(1, 6)
+        seq_info = [(rng.randint(0, 50), rng.randint(1, 40)) for _ in range(lanes)]
+        budget = rng.randint(2, 30)
+        calls = cwm_b200.prefill_chunks(seq_info, budget)
+        assert calls == ref_prefill_splits(seq_info, budget)
+        total = sum(n for _, n in seq_info)
+        # the calls tile the concatenated tokens, none exceeds the budget
+        assert calls[0][0] == 0 and calls[-1][1] == total
+        for (f0, l0, _, info0), (f1, _, _, _) in zip(calls, calls[1:]):
+            assert l0 == f1
+        for f, l, _, info in calls:
+            assert 0 < l - f <= budget and sum(n for _, n in info) == l - f
+            # a one-token lane whose end coincides with a cut is passed with zero new
+            # tokens and fed in the next call (the reference does the same)
+            assert all(n >= 0 for _, n in info)
+        # every lane ends with all its tokens cached-or-fed, positions contiguous
+        fed = {}
+        for _, _, lane0, info in calls:
+            for k, (cached, n) in enumerate(info):
+                lane = lane0 + k
+                assert cached == seq_info[lane][0] + fed.get(lane, 0)
+                fed[lane] = fed.get(lane, 0) + n
+        assert all(fed[i] == n for i, (_, n) in enumerate(seq_info))
+    with pytest.raises(ValueError):
+        cwm_b200.prefill_chunks([(0, 5)], 1)
+    with pytest.raises(ValueError):
+        cwm_b200.prefill_chunks([(0, 0)], 8)
