@@ -47,6 +47,8 @@ SIGNATURES: dict[str, tuple] = {
          c_int64, c_int64, c_int64, c_void_p],
     ),
     "cwm_paged_attn_workspace_bytes": (c_size_t, [c_int, c_int64, c_int, c_int, c_int]),
+    "cwm_paged_attn_workspace_zero_bytes": (c_size_t, [c_int, c_int]),
+    "cwm_test_hooks": (c_int, [ctypes.c_longlong, c_int]),
     "cwm_paged_attn_fwd": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -102,8 +104,17 @@ def check(code: int, what: str) -> None:
     raise CwmError(f"{what}: {msg}")
 
 
+# callables run when the status word comes back non-zero (state to re-initialise)
+on_bad_status: list = []
+
+
 def device_status(stream_ptr: int = 0) -> int:
-    """Read and clear the device status word (synchronises the stream)."""
+    """Read and clear the device status word (synchronises the stream).  A non-zero
+    word means that the output of an earlier call is not valid; the registered
+    clean-ups (``on_bad_status``) run before it is returned."""
     out = c_int32(0)
     check(load().cwm_device_status(ctypes.byref(out), stream_ptr), "cwm_device_status")
+    if out.value != 0:
+        for fn in on_bad_status:
+            fn()
     return int(out.value)

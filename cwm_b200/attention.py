@@ -14,32 +14,65 @@ from . import _lib
 from .kernels import _DTYPES, _on_device, _ptr, _require_cuda, _stream, _use_registered_op
 
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
-# batch size the cached workspace is sized for; larger batches get a fresh one
-_WS_BATCH = 16384
+_capture_workspaces: dict[int, torch.Tensor] = {}
+# problem size the cached workspace is sized for; larger ones get a fresh one
+_WS_BATCH_X_HEADS = 16384 * 8
 
 
-def workspace_for(device: torch.device, batch: int) -> torch.Tensor:
-    """Scratch buffer for ``mha_fwd`` on ``device`` (split-KV partial results and
-    the tile prefix of the decode scheduler).
+def _new_workspace(device: torch.device, batch: int, hkv: int) -> torch.Tensor:
+    lib = _lib.load()
+    need = lib.cwm_paged_attn_workspace_bytes(batch, 0, 0, hkv, 0)
+    ws = torch.empty(need, dtype=torch.uint8, device=device)
+    # the arrival counters at the head of the workspace start at zero; every
+    # call leaves them zero, so this happens once per buffer
+    ws[: lib.cwm_paged_attn_workspace_zero_bytes(batch, hkv)].zero_()
+    return ws
 
-    One buffer per device and stream is cached and shared by all calls on that
-    stream, which is safe because calls on one stream run in order.  While a CUDA
-    graph is being captured a fresh buffer is taken from the graph's pool instead,
-    so that the captured kernels never point at memory the cache could drop.
+
+def workspace_for(device: torch.device, batch: int, hkv: int = 8) -> torch.Tensor:
+    """Scratch buffer for ``mha_fwd`` on ``device`` (arrival counters and split-KV
+    partial results of the decode kernel).
+
+    Eager calls share one buffer per device and stream, which is safe because calls
+    on one stream run in order.  Calls made while a CUDA graph is being captured use
+    a second, per-device buffer that is allocated (and cleared) by the first eager
+    call on that device, outside any graph pool, and is never dropped: every graph
+    captured on the device points at it, so graphs must not be replayed
+    concurrently with each other.  A capture on a device that has not seen an eager
+    call yet takes a fresh buffer from the graph's pool for every call instead,
+    cleared by a memset node on each replay.
     """
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    fits = batch * hkv <= _WS_BATCH_X_HEADS
     if torch.cuda.is_current_stream_capturing():
-        need = _lib.load().cwm_paged_attn_workspace_bytes(batch, 0, 0, 0, 0)
-        return torch.empty(need, dtype=torch.uint8, device=device)
-    key = (device.index if device.index is not None else torch.cuda.current_device(),
-           torch.cuda.current_stream(device).cuda_stream)
+        ws = _capture_workspaces.get(index)
+        if ws is not None and fits:
+            return ws
+        return _new_workspace(device, batch, hkv)
+    if index not in _capture_workspaces:
+        _capture_workspaces[index] = _new_workspace(device, _WS_BATCH_X_HEADS // 8, 8)
+    key = (index, torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
-    if ws is not None and batch <= _WS_BATCH:
+    if fits:
+        if ws is None:
+            ws = _new_workspace(device, _WS_BATCH_X_HEADS // 8, 8)
+            _workspaces[key] = ws
         return ws
-    need = _lib.load().cwm_paged_attn_workspace_bytes(max(batch, _WS_BATCH), 0, 0, 0, 0)
+    need = _lib.load().cwm_paged_attn_workspace_bytes(batch, 0, 0, hkv, 0)
     if ws is None or ws.numel() < need:
-        ws = torch.empty(need, dtype=torch.uint8, device=device)
+        ws = _new_workspace(device, batch, hkv)
         _workspaces[key] = ws
     return ws
+
+
+def reset_workspaces() -> None:
+    """Clear the arrival counters of every cached workspace (a call that ended with
+    a device status word other than 0 may have left them non-zero)."""
+    for ws in list(_workspaces.values()) + list(_capture_workspaces.values()):
+        ws.zero_()
+
+
+_lib.on_bad_status.append(reset_workspaces)
 
 
 def _paged_attn_impl(
@@ -61,7 +94,7 @@ def _paged_attn_impl(
     lse = torch.empty((hq, total_q), dtype=torch.float32, device=query.device)
     if total_q == 0 or batch == 0:
         return out, lse
-    ws = workspace_for(query.device, batch)
+    ws = workspace_for(query.device, batch, hkv)
     with _on_device(query):
         code = _lib.load().cwm_paged_attn_fwd(
             query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(), lse.data_ptr(),

@@ -67,7 +67,6 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
         return LIB_PATH
     OBJ_DIR.mkdir(exist_ok=True)
     extra = ["-Xptxas", "-v"] if ptxas_info else []
-    extra += os.environ.get("CWM_NVCC_EXTRA", "").split()
     with concurrent.futures.ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as pool:
         objs = list(pool.map(lambda s: _compile(s, verbose or ptxas_info, extra), sources()))
     tmp = LIB_PATH.with_suffix(".so.tmp")

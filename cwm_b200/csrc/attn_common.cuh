@@ -31,18 +31,30 @@ struct AttnArgs {
   long long total_q;
   float scale_log2;  // softmax_scale * log2(e)
   int window_left;   // < 0: unbounded
-  int* prefix;       // workspace: int[batch + 1], tile prefix written by the decode kernel
+  int* counters;     // workspace: int[batch * hkv], arrivals per (sequence, KV head); all zero
+                     // between launches
   float* partial;    // workspace: split-KV partial states
   int* status;       // device status word
+  long long wait_cycles;  // limit of every bounded wait, in SM clock cycles
+  int decode_launched;    // the decode kernel runs in this call (prefill kernel: cross-check)
+  int test_drop_last;     // self-test only: each producer withholds its last tile's loads
 };
 using DecodeArgs = AttnArgs;
 
-size_t decode_workspace_bytes(int batch);
+// Split-KV workspace: arrival counters (one per sequence and KV head) followed by two
+// partial states per CTA.  The counters must be zero when a launch starts; every
+// launch leaves them zero again.
+size_t decode_workspace_bytes(int batch, int hkv);
 // max_ctas caps the persistent grid (the workspace holds two partials per CTA).
 int launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, AttnArgs a, bool bf16,
                   void* workspace, cudaStream_t stream, int max_ctas = kMaxDecodeCtas);
 // Workspace bytes for a decode grid of at most max_ctas CTAs.
-size_t decode_workspace_bytes_for(int batch, int max_ctas);
+size_t decode_workspace_bytes_for(int batch, int hkv, int max_ctas);
+// Bytes at the start of the workspace that hold the arrival counters.
+size_t decode_counter_bytes(int batch, int hkv);
+// Values of the self-test hooks (cwm_test_hooks) for the next launches.
+long long hook_wait_cycles();
+int hook_drop_last_tile();
 int launch_prefill_tc(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap,
                       AttnArgs a, bool bf16, cudaStream_t stream);
 

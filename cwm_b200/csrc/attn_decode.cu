@@ -13,8 +13,12 @@
 // warp-shuffle row reductions), and keep their own running (max, sum, O).  When a
 // (sequence, KV head) segment ends, the four warp states are merged through
 // shared memory; a segment that lies wholly inside one CTA is written straight to
-// the output, otherwise the CTA leaves a partial (max, sum, O) in the workspace
-// and the combine kernel merges the partials of that segment in a fixed order.
+// the output, otherwise the CTA leaves a partial (max, sum, O) in the workspace and
+// bumps the segment's arrival counter; the CTA that arrives last merges the partials
+// of that segment, always in CTA order (so the result does not depend on timing),
+// writes the output and resets the counter.  One launch, no second kernel.
+#include <atomic>
+
 #include "attn_common.cuh"
 
 namespace cwm {
@@ -140,6 +144,7 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
   uint64_t* empty_bar = full_bar + kStages;
   int* prefix = reinterpret_cast<int*>(empty_bar + kStages);
   __shared__ int abort_flag;
+  __shared__ int merge_flag;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -156,14 +161,16 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     prefetch_tensormap(&vmap);
   }
   // Launched with programmatic serialization: the CTAs may be resident while the
-  // previous kernel (typically the rotary + cache write, or the combine step of the
-  // previous call, which still reads the workspace) is finishing.  Nothing that
-  // another kernel may have written is read before this returns; the combine kernel
-  // of this call may become resident right away.
+  // previous kernel (typically the rotary + cache write, or the previous attention
+  // call, which still uses the workspace) is finishing.  Nothing that another kernel
+  // may have written is read, and nothing is written, before this returns.
   pdl_wait();
   pdl_launch_dependents();
+  const long long wait_limit = a.wait_cycles;
   // tiles per sequence -> exclusive prefix over sequences (times KV heads)
-  for (int b = tid; b < a.batch; b += kThreads) prefix[b + 1] = seq_info(a, b).ntiles * a.hkv;
+  for (int b = tid; b < a.batch; b += kThreads) {
+    prefix[b + 1] = seq_info(a, b).ntiles * a.hkv;
+  }
   if (tid == 0) prefix[0] = 0;
   __syncthreads();
   if (warp == 0) {
@@ -181,10 +188,21 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     }
   }
   __syncthreads();
-  const int total = prefix[a.batch];
-  if (blockIdx.x == 0) {
-    for (int b = tid; b <= a.batch; b += kThreads) a.prefix[b] = prefix[b];
+  // decode sequences without any key (padded lanes of a batch bucket): zero output
+  for (int b = blockIdx.x; b < a.batch; b += gridDim.x) {
+    if (prefix[b + 1] != prefix[b]) continue;
+    const int q0 = a.cu_q[b];
+    if (a.cu_q[b + 1] - q0 != 1) continue;
+    uint32_t* orow = reinterpret_cast<uint32_t*>(a.out) +
+                     static_cast<long long>(q0) * a.hq * (kHeadDim / 2);
+    for (int i = tid; i < a.hq * (kHeadDim / 2); i += kThreads) orow[i] = 0u;
+    if (a.lse != nullptr) {
+      for (int hh = tid; hh < a.hq; hh += kThreads) {
+        a.lse[static_cast<long long>(hh) * a.total_q + q0] = -INFINITY;
+      }
+    }
   }
+  const int total = prefix[a.batch];
   const int per = (total + gridDim.x - 1) / gridDim.x;
   const int g_begin = min(total, static_cast<int>(blockIdx.x) * per);
   const int g_end = min(total, g_begin + per);
@@ -220,8 +238,10 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
         if (lane == 0) {
           const int s = issued % kStages;
           const uint32_t ph = (issued / kStages) & 1;
-          if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1)) {
+          if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, wait_limit)) {
             ok = false;
+          } else if (a.test_drop_last && g0 + j == g_end - 1) {
+            // self-test: the last tile never arrives, so the consumers' wait runs out
           } else {
             uint8_t* st = stages + s * kStageBytes;
             mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
@@ -247,7 +267,7 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
       for (int i = first; i < issued; ++i) {
         const int s = i % kStages;
         const uint32_t ph = (i / kStages) & 1;
-        if (!mbar_wait_bounded(&full_bar[s], ph)) {
+        if (!mbar_wait_bounded(&full_bar[s], ph, wait_limit)) {
           atomicOr(a.status, DEV_WAIT_TIMEOUT);
           break;
         }
@@ -281,7 +301,8 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
   };
   load_q();
 
-  // Merge the four warp states and write the segment's result or partial.
+  // Merge the four warp states and write the segment's result, or leave a partial
+  // and, if this CTA is the last of the segment's CTAs to do so, merge them all.
   auto flush = [&](int seg_end) {
     // reduce the per-thread partial sums over the 4 lanes of a head
     f.l += __shfl_xor_sync(0xffffffffu, f.l, 1);
@@ -293,15 +314,71 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     named_bar_sync(1, kConsumerWarps * 32);
     if (warp == 1) frag_store(f, merge_buf, lane);
     named_bar_sync(1, kConsumerWarps * 32);
+    const bool complete = seg_start >= g_begin && seg_end <= g_end;  // same in every warp
+    // CTAs that hold a part of this segment: first .. last
+    const int c_first = seg_start / per;
+    const int c_last = (seg_start + si.ntiles - 1) / per;
     if (warp == 0) {
       frag_merge(f, merge_buf, lane);
-      const bool complete = seg_start >= g_begin && seg_end <= g_end;
       if (complete) {
         frag_write_out<kBf16>(f, a, si.qtok, h, lane);
       } else {
         const int slot = seg_start <= g_begin ? 0 : 1;
         frag_store(f, a.partial + (static_cast<long long>(blockIdx.x) * 2 + slot) * kPartialFloats,
                    lane);
+        __threadfence();  // the partial is visible device-wide before the arrival counts
+        __syncwarp();
+        if (lane == 0) {
+          int* counter = a.counters + b * a.hkv + h;
+          const int arrived = atomicAdd(counter, 1);
+          const int last = arrived == c_last - c_first ? 1 : 0;
+          if (last) *counter = 0;  // every CTA of the segment has arrived: ready for the next launch
+          __threadfence();
+          merge_flag = last;
+        }
+      }
+    }
+    if (complete) return;
+    named_bar_sync(1, kConsumerWarps * 32);
+    if (merge_flag == 0) return;
+    // This CTA arrived last: merge the partials of CTAs c_first .. c_last in that
+    // order.  Warp w owns output columns 32 w .. 32 w + 31 of every head.  Two passes
+    // with independent loads (the maxima, then the weighted sums), past L1.
+    auto partial_of = [&](int cta) {
+      const int slot = seg_start <= cta * per ? 0 : 1;
+      return a.partial + (static_cast<long long>(cta) * 2 + slot) * kPartialFloats;
+    };
+    float m = -INFINITY;
+#pragma unroll 4
+    for (int cta = c_first; cta <= c_last; ++cta) m = fmaxf(m, __ldcg(partial_of(cta) + 32 * 32 + lane));
+    const float mu = m == -INFINITY ? 0.f : m;
+    float l = 0.f;
+    float o[4][2];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j][0] = o[j][1] = 0.f;
+#pragma unroll 4
+    for (int cta = c_first; cta <= c_last; ++cta) {
+      const float* buf = partial_of(cta);
+      const float w = fast_exp2(__ldcg(buf + 32 * 32 + lane) - mu);
+      l = fmaf(__ldcg(buf + 33 * 32 + lane), w, l);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        o[j][0] = fmaf(__ldcg(buf + (2 * (4 * warp + j)) * 32 + lane), w, o[j][0]);
+        o[j][1] = fmaf(__ldcg(buf + (2 * (4 * warp + j) + 1) * 32 + lane), w, o[j][1]);
+      }
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    if (g < a.group) {
+      const int head = h * a.group + g;
+      uint32_t* orow = reinterpret_cast<uint32_t*>(a.out) +
+                       (static_cast<long long>(si.qtok) * a.hq + head) * (kHeadDim / 2);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        orow[(4 * warp + j) * 4 + c] = pack2<kBf16>(o[j][0] * inv, o[j][1] * inv);
+      }
+      if (a.lse != nullptr && warp == 0 && c == 0) {
+        a.lse[static_cast<long long>(head) * a.total_q + si.qtok] =
+            l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
       }
     }
   };
@@ -315,13 +392,27 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
   for (int gi = g_begin; gi < g_end; ++gi, ++it) {
     const int s = it % kStages;
     const uint32_t ph = (it / kStages) & 1;
-    if (ok && (!mbar_wait_bounded(&full_bar[s], ph) || *((volatile int*)&abort_flag))) {
+    if (ok && (!mbar_wait_bounded(&full_bar[s], ph, wait_limit) || *((volatile int*)&abort_flag))) {
       ok = false;
       abort_flag = 1;
     }
     const uint32_t st = smem_u32(stages + s * kStageBytes);
     const int tok0 = (si.tile0 + t) * kTile + warp * 16;
     if (ok && tok0 + 16 > si.lo && tok0 < si.ctx) {
+      if (tok0 + 16 > si.ctx) {
+        // Rows at or beyond the end of the context hold whatever the page held before
+        // (possibly Inf or NaN, which P = 0 would not cancel): clear their V values.
+        const int r = lane & 15;
+        if (tok0 + r >= si.ctx) {
+          uint4* dst = reinterpret_cast<uint4*>(stages + s * kStageBytes +
+                                                (2 + (lane >> 4)) * kBoxBytes +
+                                                (warp * 16 + r) * 128);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        fence_proxy_async_smem();  // before the producer's next TMA write to this stage
+        __syncwarp();
+      }
       // ---- S = Q K^T for 16 tokens: two n-tiles of 8 tokens
       float sacc[2][4];
 #pragma unroll
@@ -417,79 +508,6 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
   if (!ok && lane == 0) atomicOr(a.status, DEV_WAIT_TIMEOUT);
 }
 
-// One CTA of four warps per (KV head, sequence): merge the partials that the
-// persistent CTAs left for this segment and write the result; also writes zeros for
-// decode sequences without any key.  Warp w owns output columns 32 w .. 32 w + 31 of
-// every head.  Two passes over the partials, both with independent loads (first the
-// maxima, then the weighted sums), always in CTA order, so the result does not
-// depend on timing.
-template <bool kBf16>
-__global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeArgs a, int grid_main) {
-  const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
-  const int b = blockIdx.x / a.hkv;
-  const int h = blockIdx.x - b * a.hkv;
-  pdl_wait();                // the decode kernel's partials and prefix
-  pdl_launch_dependents();   // the next kernel may become resident meanwhile
-  const int q0 = a.cu_q[b];
-  if (a.cu_q[b + 1] - q0 != 1) return;
-  const int nt = (a.prefix[b + 1] - a.prefix[b]) / a.hkv;
-  const int g = lane >> 2;
-  const int c = lane & 3;
-  const int head = h * a.group + g;
-  uint32_t* orow = reinterpret_cast<uint32_t*>(a.out) +
-                   (static_cast<long long>(q0) * a.hq + head) * (kHeadDim / 2);
-  float* lse = a.lse != nullptr && warp == 0 && c == 0 && g < a.group
-                   ? a.lse + static_cast<long long>(head) * a.total_q + q0
-                   : nullptr;
-  if (nt == 0) {
-    if (g < a.group) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) orow[(4 * warp + j) * 4 + c] = 0u;
-    }
-    if (lse != nullptr) *lse = -INFINITY;
-    return;
-  }
-  const int total = a.prefix[a.batch];
-  const int per = (total + grid_main - 1) / grid_main;
-  const int s0 = a.prefix[b] + h * nt;
-  const int s1 = s0 + nt;
-  const int c_first = s0 / per;
-  const int c_last = (s1 - 1) / per;
-  if (c_first == c_last) return;  // written directly by its CTA
-  auto partial_of = [&](int cta) {
-    const int slot = s0 <= cta * per ? 0 : 1;
-    return a.partial + (static_cast<long long>(cta) * 2 + slot) * kPartialFloats;
-  };
-  float m = -INFINITY;
-#pragma unroll 4
-  for (int cta = c_first; cta <= c_last; ++cta) m = fmaxf(m, partial_of(cta)[32 * 32 + lane]);
-  const float mu = m == -INFINITY ? 0.f : m;
-  float l = 0.f;
-  float o[4][2];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) o[j][0] = o[j][1] = 0.f;
-#pragma unroll 4
-  for (int cta = c_first; cta <= c_last; ++cta) {
-    const float* buf = partial_of(cta);
-    const float w = fast_exp2(buf[32 * 32 + lane] - mu);
-    l = fmaf(buf[33 * 32 + lane], w, l);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      o[j][0] = fmaf(buf[(2 * (4 * warp + j)) * 32 + lane], w, o[j][0]);
-      o[j][1] = fmaf(buf[(2 * (4 * warp + j) + 1) * 32 + lane], w, o[j][1]);
-    }
-  }
-  const float inv = l > 0.f ? 1.f / l : 0.f;
-  if (g < a.group) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      orow[(4 * warp + j) * 4 + c] = pack2<kBf16>(o[j][0] * inv, o[j][1] * inv);
-    }
-  }
-  if (lse != nullptr) *lse = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
-}
-
 }  // namespace
 
 size_t decode_smem_bytes(int batch) {
@@ -497,20 +515,26 @@ size_t decode_smem_bytes(int batch) {
          2 * kStages * sizeof(uint64_t) + (static_cast<size_t>(batch) + 1) * sizeof(int);
 }
 
-size_t decode_workspace_bytes_for(int batch, int max_ctas) {
-  const size_t prefix_bytes = ((static_cast<size_t>(batch) + 1) * sizeof(int) + 255) / 256 * 256;
-  return prefix_bytes + static_cast<size_t>(max_ctas) * 2 * kPartialFloats * sizeof(float);
+size_t decode_counter_bytes(int batch, int hkv) {
+  return (static_cast<size_t>(batch) * static_cast<size_t>(hkv) * sizeof(int) + 255) / 256 * 256;
 }
 
-size_t decode_workspace_bytes(int batch) {
-  return decode_workspace_bytes_for(batch, kMaxDecodeCtas);
+size_t decode_workspace_bytes_for(int batch, int hkv, int max_ctas) {
+  return decode_counter_bytes(batch, hkv) +
+         static_cast<size_t>(max_ctas) * 2 * kPartialFloats * sizeof(float);
+}
+
+size_t decode_workspace_bytes(int batch, int hkv) {
+  return decode_workspace_bytes_for(batch, hkv, kMaxDecodeCtas);
 }
 
 int launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, DecodeArgs a, bool bf16,
                   void* workspace, cudaStream_t stream, int max_ctas) {
-  const size_t prefix_bytes = ((static_cast<size_t>(a.batch) + 1) * sizeof(int) + 255) / 256 * 256;
-  a.prefix = static_cast<int*>(workspace);
-  a.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + prefix_bytes);
+  a.counters = static_cast<int*>(workspace);
+  a.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) +
+                                       decode_counter_bytes(a.batch, a.hkv));
+  a.wait_cycles = hook_wait_cycles();
+  a.test_drop_last = hook_drop_last_tile();
   const size_t smem = decode_smem_bytes(a.batch);
   if (smem > 110 * 1024) {
     set_error("paged_attn: batch %d too large for the decode scheduler", a.batch);
@@ -519,19 +543,16 @@ int launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, DecodeArgs a
   int grid = 2 * sm_count();
   if (grid > max_ctas) grid = max_ctas;
   // the opt-in to large dynamic shared memory is per device and per kernel
-  static bool attr_set[64][2] = {};
+  static std::atomic<bool> attr_set[64][2];
   auto main_k = bf16 ? decode_kernel<true> : decode_kernel<false>;
   int dev = 0;
   CWM_CUDA_CHECK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !attr_set[dev][bf16 ? 1 : 0]) {
+  if (dev < 0 || dev >= 64 || !attr_set[dev][bf16 ? 1 : 0].load(std::memory_order_acquire)) {
     CWM_CUDA_CHECK(cudaFuncSetAttribute(main_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         110 * 1024));
-    if (dev >= 0 && dev < 64) attr_set[dev][bf16 ? 1 : 0] = true;
+    if (dev >= 0 && dev < 64) attr_set[dev][bf16 ? 1 : 0].store(true, std::memory_order_release);
   }
   CWM_CUDA_CHECK(launch_pdl(main_k, dim3(grid), dim3(kThreads), smem, stream, kmap, vmap, a));
-  const int cgrid = a.batch * a.hkv;
-  auto combine_k = bf16 ? decode_combine_kernel<true> : decode_combine_kernel<false>;
-  CWM_CUDA_CHECK(launch_pdl(combine_k, dim3(cgrid), dim3(128), 0, stream, a, grid));
   CWM_CUDA_CHECK(cudaGetLastError());
   return CWM_OK;
 }

@@ -21,6 +21,7 @@
 // overlaps the matrix products of the other.  KV tiles wholly above the causal
 // diagonal or wholly left of the sliding window are never loaded; only edge tiles
 // are masked.  Every mbarrier wait is bounded.  Needs no scratch memory.
+#include <atomic>
 #include <type_traits>
 
 #include "attn_common.cuh"
@@ -37,11 +38,9 @@ constexpr int kTileBytes = 128 * 256;  // [2 halves of 64 elements][128 rows][12
 constexpr int kHalfBytes = 128 * 128;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.f;  // log2 domain
-// Of every four pairs of scores, this many take the polynomial exp2.
-#ifndef CWM_POLY_PAIRS
-#define CWM_POLY_PAIRS 1
-#endif
-constexpr int kPolyPairsOfFour = CWM_POLY_PAIRS;
+// Of every four pairs of scores, this many take the polynomial exp2 (more than one
+// makes the softmax warps issue-bound).
+constexpr int kPolyPairsOfFour = 1;
 
 struct Bars {
   uint64_t q_full;
@@ -57,19 +56,6 @@ struct QTile {
   int lo;    // first KV tile
   int hi;    // last KV tile (hi < lo: nothing visible)
 };
-
-#ifdef CWM_TRACE
-// Development aid: cycle stamps of the first CTA, read back with cwm_trace_read().
-__device__ long long g_trace[4][64][8];
-#define CWM_STAMP(role, iter, slot)                                                   \
-  do {                                                                                \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (iter) < 64) g_trace[role][iter][slot] = clock64(); \
-  } while (0)
-#else
-#define CWM_STAMP(role, iter, slot) \
-  do {                              \
-  } while (0)
-#endif
 
 __device__ __forceinline__ bool visible(int key, int pos, int window_left) {
   return key <= pos && (window_left < 0 || key >= pos - window_left);
@@ -113,11 +99,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
   // kernel may have written is read before the previous kernel has completed.
   pdl_wait();
   pdl_launch_dependents();
+  const long long wait_limit = a.wait_cycles;
   // work units per sequence: 128-row blocks (head pairs) or 256-row double blocks
   const int unit_rows = pair_heads ? kBM : 2 * kBM;
   for (int b = tid; b < a.batch; b += kThreadsTc) {
     const int t = a.cu_q[b + 1] - a.cu_q[b];
     blk_prefix[b + 1] = t > 1 ? (t + unit_rows - 1) / unit_rows : 0;
+    // a one-query sequence although the caller's bounds said there was none: the
+    // decode kernel was not launched, so its output rows are not computed
+    if (t == 1 && !a.decode_launched && blockIdx.x == 0 && blockIdx.y == 0) {
+      atomicOr(a.status, DEV_BAD_POS);
+    }
   }
   if (tid == 0) blk_prefix[0] = 0;
   __syncthreads();
@@ -137,6 +129,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
   }
   __syncthreads();
   const int total_units = blk_prefix[a.batch];
+  // more query blocks than the grid was sized for (max_seqlen_q below the true
+  // maximum): the first blocks are not computed
+  if (total_units > static_cast<int>(gridDim.y) && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
+    atomicOr(a.status, DEV_BAD_POS);
+  }
   const int unit = total_units - 1 - static_cast<int>(blockIdx.y);  // heavier blocks first
   if (unit < 0) return;
   int b;
@@ -241,8 +238,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
           if (lane == 0) {
             const int s = issued % kStages;
             const uint32_t ph = (issued / kStages) & 1;
-            if (!mbar_wait_bounded(&bars->k_empty[s], ph ^ 1)) {
+            if (!mbar_wait_bounded(&bars->k_empty[s], ph ^ 1, wait_limit)) {
               ok = false;
+            } else if (a.test_drop_last && i0 + j == n_tiles - 1) {
+              // self-test: the last tile never arrives, so the waits for it run out
             } else {
               uint8_t* kd = k_smem + s * kTileBytes;
               mbar_arrive_expect_tx(&bars->k_full[s], kTileBytes);
@@ -250,7 +249,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
               tma_load_2d(kd + 64 * 128, &kmap, x, rb, &bars->k_full[s]);
               tma_load_2d(kd + kHalfBytes, &kmap, x + 64, ra, &bars->k_full[s]);
               tma_load_2d(kd + kHalfBytes + 64 * 128, &kmap, x + 64, rb, &bars->k_full[s]);
-              if (!mbar_wait_bounded(&bars->v_empty[s], ph ^ 1)) {
+              if (!mbar_wait_bounded(&bars->v_empty[s], ph ^ 1, wait_limit)) {
                 ok = false;
               } else {
                 uint8_t* vd = v_smem + s * kTileBytes;
@@ -271,10 +270,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         if (!ok) atomicOr(a.status, DEV_WAIT_TIMEOUT);
         // do not leave while copies are in flight
         const int first = issued > kStages ? issued - kStages : 0;
-        bool drained = mbar_wait_bounded(&bars->q_full, 0);
+        bool drained = mbar_wait_bounded(&bars->q_full, 0, wait_limit);
         for (int i = first; i < issued && drained; ++i) {
-          drained = mbar_wait_bounded(&bars->k_full[i % kStages], (i / kStages) & 1) &&
-                    mbar_wait_bounded(&bars->v_full[i % kStages], (i / kStages) & 1);
+          drained = mbar_wait_bounded(&bars->k_full[i % kStages], (i / kStages) & 1, wait_limit) &&
+                    mbar_wait_bounded(&bars->v_full[i % kStages], (i / kStages) & 1, wait_limit);
         }
         if (!drained) atomicOr(a.status, DEV_WAIT_TIMEOUT);
       }
@@ -308,7 +307,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                        (first && kk == 0) ? 0u : 1u);
         }
       };
-      bool ok = mbar_wait_bounded(&bars->q_full, 0) && mbar_wait_bounded(&bars->k_full[0], 0);
+      bool ok = mbar_wait_bounded(&bars->q_full, 0, wait_limit) && mbar_wait_bounded(&bars->k_full[0], 0, wait_limit);
       if (ok) {
         tc05::fence_after_sync();
         if (active(0, 0)) issue_s(0, 0);
@@ -321,26 +320,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         const uint32_t ph = (j / kStages) & 1;
         const int s1 = (j + 1) % kStages;
         const bool more = j + 1 < n_tiles;
-        ok = mbar_wait_bounded(&bars->v_full[s], ph);
-        if (ok && more) ok = mbar_wait_bounded(&bars->k_full[s1], ((j + 1) / kStages) & 1);
+        ok = mbar_wait_bounded(&bars->v_full[s], ph, wait_limit);
+        if (ok && more) ok = mbar_wait_bounded(&bars->k_full[s1], ((j + 1) / kStages) & 1, wait_limit);
         if (!ok) break;
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (active(x, j)) {
-            CWM_STAMP(2 + x, j, 0);
-            if (!mbar_wait_bounded(&bars->p_full[x], pcnt[x] & 1)) {
+            if (!mbar_wait_bounded(&bars->p_full[x], pcnt[x] & 1, wait_limit)) {
               ok = false;
               break;
             }
             tc05::fence_after_sync();
-            CWM_STAMP(2 + x, j, 1);
             issue_pv(x, s, pcnt[x] == 0);
-            CWM_STAMP(2 + x, j, 2);
             ++pcnt[x];
             if (lo + j == qt[x].hi) tc05::commit(&bars->o_full[x]);
           }
           if (more && active(x, j + 1)) issue_s(x, s1);
-          CWM_STAMP(2 + x, j, 3);
         }
         if (!ok) break;
         tc05::commit(&bars->v_empty[s]);
@@ -369,13 +364,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 
     for (int i = 0; i < nx && ok; ++i) {
       const int k0 = (qt[x].lo + i) * kBN;
-      if (quarter == 0 && lane == 0) CWM_STAMP(x, i, 0);
-      if (!mbar_wait_bounded(&bars->s_full[x], i & 1)) {
+      if (!mbar_wait_bounded(&bars->s_full[x], i & 1, wait_limit)) {
         ok = false;
         break;
       }
       tc05::fence_after_sync();
-      if (quarter == 0 && lane == 0) CWM_STAMP(x, i, 1);
       const bool full = k0 + kBN - 1 <= wpos_lo && (wl < 0 || k0 >= wpos_hi - wl);
 
       // ---- the 128 scores of the row: four loads in flight, one wait, kept in
@@ -414,7 +407,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                    max3(max3(part[3], part[4], part[5]), part[6], part[7]));
       }
 
-      if (quarter == 0 && lane == 0) CWM_STAMP(x, i, 2);
       // ---- running maximum, updated lazily
       const float m_new = fmaxf(m_used, mx * a.scale_log2);
       const bool grow = m_new - m_used > kRescaleThreshold;  // false when both are -inf
@@ -439,7 +431,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
       }
       const float mu = m_used == -INFINITY ? 0.f : m_used;
 
-      if (quarter == 0 && lane == 0) CWM_STAMP(x, i, 3);
       // ---- P = exp2(S * scale - m), written over S as packed 16-bit pairs
       float psum = 0.f;
       {
@@ -470,9 +461,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
               acc[(e >> 1) & 3] = add2(acc[(e >> 1) & 3], t);
               packed[e >> 1] = pack2<kBf16>(t.x, t.y);
             }
-            if (c == 0 && quarter == 0 && lane == 0) CWM_STAMP(x, i, 5);
             tc05::st16(s_addr + c * 16, packed);
-            if (c == 0 && quarter == 0 && lane == 0) CWM_STAMP(x, i, 6);
           }
         };
         if (full) {
@@ -484,14 +473,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         psum = s01.x + s01.y;
       }
       l += psum;
-      if (quarter == 0 && lane == 0) CWM_STAMP(x, i, 4);
       tc05::wait_st();
       tc05::fence_before_sync();
       mbar_arrive(&bars->p_full[x]);
     }
 
     // ---- epilogue: O / l -> global
-    if (ok && nx > 0) ok = mbar_wait_bounded(&bars->o_full[x], 0);
+    if (ok && nx > 0) ok = mbar_wait_bounded(&bars->o_full[x], 0, wait_limit);
     if (!ok) {
       if (lane == 0) atomicOr(a.status, DEV_WAIT_TIMEOUT);
     } else {
@@ -540,12 +528,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 
 }  // namespace
 
-#ifdef CWM_TRACE
-extern "C" __attribute__((visibility("default"))) int cwm_trace_read(void* host, size_t bytes) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace, bytes));
-}
-#endif
-
 size_t prefill_tc_smem_bytes(int batch) {
   return 2 * kTileBytes + 2 * kStages * kTileBytes + sizeof(Bars) + 2 * sizeof(uint32_t) +
          (static_cast<size_t>(batch) + 1) * sizeof(int);
@@ -560,13 +542,15 @@ int launch_prefill_tc(const CUtensorMap& qmap, const CUtensorMap& kmap, const CU
     return CWM_ERR_UNSUPPORTED;
   }
   auto k = bf16 ? prefill_tc_kernel<true> : prefill_tc_kernel<false>;
-  static bool attr_set[64][2] = {};
+  a.wait_cycles = hook_wait_cycles();
+  a.test_drop_last = hook_drop_last_tile();
+  static std::atomic<bool> attr_set[64][2];
   int dev = 0;
   CWM_CUDA_CHECK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !attr_set[dev][bf16 ? 1 : 0]) {
+  if (dev < 0 || dev >= 64 || !attr_set[dev][bf16 ? 1 : 0].load(std::memory_order_acquire)) {
     CWM_CUDA_CHECK(
         cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    if (dev >= 0 && dev < 64) attr_set[dev][bf16 ? 1 : 0] = true;
+    if (dev >= 0 && dev < 64) attr_set[dev][bf16 ? 1 : 0].store(true, std::memory_order_release);
   }
   const int pair_heads = a.group % 2 == 0 ? 1 : 0;
   const int unit_rows = pair_heads ? kBM : 2 * kBM;

@@ -5,6 +5,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 #include <vector>
 
@@ -40,18 +41,26 @@ int* status_word() {
 }
 
 int sm_count() {
-  static int counts[kMaxDevices] = {0};
+  static std::atomic<int> counts[kMaxDevices];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
-  if (counts[dev] == 0) {
-    int n = 0;
+  int n = counts[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
       n = 148;
     }
-    counts[dev] = n;
+    counts[dev].store(n, std::memory_order_relaxed);
   }
-  return counts[dev];
+  return n;
 }
+
+namespace {
+std::atomic<long long> g_hook_wait_cycles{kDefaultWaitCycles};
+std::atomic<int> g_hook_drop_last{0};
+}  // namespace
+
+long long hook_wait_cycles() { return g_hook_wait_cycles.load(std::memory_order_relaxed); }
+int hook_drop_last_tile() { return g_hook_drop_last.load(std::memory_order_relaxed); }
 
 namespace {
 
@@ -94,7 +103,7 @@ int get_kv_map(const void* base, long long inner, long long rows, long long stri
   static std::mutex mu;
   static std::vector<std::pair<MapKey, CUtensorMap>> cache;
   int dev = 0;
-  cudaGetDevice(&dev);
+  CWM_CUDA_CHECK(cudaGetDevice(&dev));
   const MapKey key{base, inner, rows, stride_bytes, dtype, box_rows, dev};
   if (use_cache) {
     std::lock_guard<std::mutex> lock(mu);
@@ -171,13 +180,23 @@ extern "C" int cwm_device_status(int32_t* host_out, void* stream) {
   return CWM_OK;
 }
 
+extern "C" int cwm_test_hooks(long long wait_limit_cycles, int drop_last_tile) {
+  g_hook_wait_cycles.store(wait_limit_cycles > 0 ? wait_limit_cycles : kDefaultWaitCycles,
+                           std::memory_order_relaxed);
+  g_hook_drop_last.store(drop_last_tile ? 1 : 0, std::memory_order_relaxed);
+  return CWM_OK;
+}
+
 extern "C" size_t cwm_paged_attn_workspace_bytes(int batch, int64_t total_q, int hq, int hkv,
                                                  int d) {
   (void)total_q;
   (void)hq;
-  (void)hkv;
   (void)d;
-  return decode_workspace_bytes(batch < 0 ? 0 : batch);
+  return decode_workspace_bytes(batch < 0 ? 0 : batch, hkv > 0 ? hkv : 1);
+}
+
+extern "C" size_t cwm_paged_attn_workspace_zero_bytes(int batch, int hkv) {
+  return decode_counter_bytes(batch < 0 ? 0 : batch, hkv > 0 ? hkv : 1);
 }
 
 extern "C" int cwm_paged_attn_fwd(const void* q, const void* k, const void* v, void* out,
@@ -236,7 +255,7 @@ extern "C" int cwm_paged_attn_fwd(const void* q, const void* k, const void* v, v
   // has exactly one query, so the decode kernel has nothing to do.
   const bool may_decode = !(max_seqlen_q > 1 && total_q == static_cast<int64_t>(batch) * max_seqlen_q);
   if (may_decode) {
-    const size_t need = decode_workspace_bytes(batch);
+    const size_t need = decode_workspace_bytes(batch, hkv);
     if (workspace == nullptr || workspace_bytes < need) {
       set_error("paged_attn: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
       return CWM_ERR_WORKSPACE;
@@ -276,6 +295,7 @@ extern "C" int cwm_paged_attn_fwd(const void* q, const void* k, const void* v, v
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
   a.window_left = window_left;
   a.status = status;
+  a.decode_launched = may_decode ? 1 : 0;
   auto st = static_cast<cudaStream_t>(stream);
   const bool bf16 = dtype == CWM_BF16;
   if (may_decode) {
@@ -306,13 +326,15 @@ extern "C" int cwm_paged_attn_fwd(const void* q, const void* k, const void* v, v
 namespace cwm {
 namespace {
 
-// Sized for kNoAllocMaxBatch sequences and a persistent grid of kNoAllocMaxCtas
-// CTAs (two per SM on a 148-SM B200, with headroom to 152 SMs): about 2.6 MB
-// that every GPU holds from the moment it loads the library until exit.
+// Sized for kNoAllocMaxBatch sequences with up to kNoAllocMaxKvHeads KV heads (the
+// arrival counters) and a persistent grid of kNoAllocMaxCtas CTAs (two per SM on a
+// 148-SM B200, with headroom to 152 SMs): about 2.7 MB that every GPU holds from
+// the moment it loads the library until exit.
 constexpr int kNoAllocMaxBatch = CWM_NOALLOC_MAX_BATCH;
+constexpr int kNoAllocMaxKvHeads = 16;
 constexpr int kNoAllocMaxCtas = 304;
 constexpr size_t kNoAllocScratchBytes =
-    ((static_cast<size_t>(kNoAllocMaxBatch) + 1) * sizeof(int) + 255) / 256 * 256 +
+    static_cast<size_t>(kNoAllocMaxBatch) * kNoAllocMaxKvHeads * sizeof(int) +
     static_cast<size_t>(kNoAllocMaxCtas) * 2 * 34 * 32 * sizeof(float);
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
@@ -388,8 +410,9 @@ extern "C" int cwm_paged_attn_decode_noalloc(const void* q, const void* k, const
   void* scratch = nullptr;
   int rc = noalloc_scratch(&scratch);
   if (rc != CWM_OK) return rc;
-  if (decode_workspace_bytes_for(batch, kNoAllocMaxCtas) > kNoAllocScratchBytes) {
-    set_error("paged_attn_decode_noalloc: internal scratch sizing error");
+  if (decode_workspace_bytes_for(batch, hkv, kNoAllocMaxCtas) > kNoAllocScratchBytes) {
+    set_error("paged_attn_decode_noalloc: %d sequences x %d KV heads exceed the built-in "
+              "scratch (at most %d x %d)", batch, hkv, kNoAllocMaxBatch, kNoAllocMaxKvHeads);
     return CWM_ERR_WORKSPACE;
   }
   int* status = status_word();
@@ -426,9 +449,14 @@ extern "C" int cwm_paged_attn_decode_noalloc(const void* q, const void* k, const
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
   a.window_left = window_left;
   a.status = status;
-  // Nothing in the scratch has to start at zero: the tile prefix is rewritten in
-  // full by every launch, and the combine step reads only the partial slots that
-  // this launch wrote.
+  a.decode_launched = 1;
+  // The arrival counters at the head of the scratch must be zero when the kernel
+  // starts.  A launch that ran to its end leaves them zero, but the array is shared
+  // by every caller on this device and outlives failed launches, so they are cleared
+  // here on the caller's stream (a memset node, not an allocation).  The partial
+  // states behind them need no clearing: a launch reads only slots it wrote itself.
+  CWM_CUDA_CHECK(cudaMemsetAsync(scratch, 0, decode_counter_bytes(batch, hkv),
+                                 static_cast<cudaStream_t>(stream)));
   return launch_decode(kmap, vmap, a, dtype == CWM_BF16, scratch,
                        static_cast<cudaStream_t>(stream), kNoAllocMaxCtas);
 }

@@ -99,9 +99,28 @@ CWM_API int cwm_rope_kv_write(void* xq, void* xk, const void* xv, void* cache_k,
                       int64_t page_tbl_cols, int64_t cache_stride, int64_t cache_rows,
                       void* stream);
 
-/* Bytes of scratch that cwm_paged_attn_fwd needs for this problem size (split-KV
- * partial results and scheduling prefixes).  Depends on static sizes only. */
+/* Bytes of scratch that cwm_paged_attn_fwd needs for this problem size (arrival
+ * counters and split-KV partial results of the decode kernel).  Depends on static
+ * sizes only; grows with batch * hkv. */
 CWM_API size_t cwm_paged_attn_workspace_bytes(int batch, int64_t total_q, int hq, int hkv, int d);
+
+/* The first cwm_paged_attn_workspace_zero_bytes(batch, hkv) bytes of a workspace
+ * (the arrival counters) must be zero when cwm_paged_attn_fwd is first given it:
+ * clear them once after allocating.  Every call that completes leaves them zero,
+ * so a workspace can be reused by later calls (on one stream, or otherwise ordered)
+ * and by CUDA-graph replays without clearing.  Clear them again after a call for
+ * which cwm_device_status reported bit 2. */
+CWM_API size_t cwm_paged_attn_workspace_zero_bytes(int batch, int hkv);
+
+/* Self-test hooks (process-wide, for the library's own tests; not part of the
+ * reference's interface).  wait_limit_cycles: limit of the bounded waits inside the
+ * attention kernels, in SM clock cycles (<= 0 restores the default of about two
+ * seconds).  drop_last_tile != 0: the loader warp of every CTA withholds the loads
+ * of its last K/V tile, so that the waits for that tile run out and the kernels take
+ * their give-up path (status bit 2, output invalid) instead of computing; no memory
+ * access is made that a normal launch would not make.  Applies to launches made
+ * after the call. */
+CWM_API int cwm_test_hooks(long long wait_limit_cycles, int drop_last_tile);
 
 /* Variable-length paged-KV grouped-query attention, causal, with an optional
  * sliding window.  Replaces the call
@@ -120,7 +139,20 @@ CWM_API size_t cwm_paged_attn_workspace_bytes(int batch, int64_t total_q, int hq
  * read.  lse (nullable): float32 [hq, total_q], natural log.  All lengths are
  * read on the device, so the launch is valid for any lengths within the static
  * bounds max_seqlen_q / max_seqlen_k.  Sequences with one query are served by
- * the split-KV decode kernel, the others by the tensor-core prefill kernel. */
+ * the split-KV decode kernel, the others by the tensor-core prefill kernel.
+ *
+ * Limits (CWM_ERR_UNSUPPORTED otherwise): d == 128; bf16 or fp16; hq / hkv <= 8;
+ * page_size a multiple of 64; num_pages * page_size < 2^31; batch up to about
+ * 1300 sequences (the schedulers keep one int per sequence in shared memory).
+ * max_seqlen_q must be at least the true maximum of the query counts: the launch
+ * grid is sized from it, and when total_q == batch * max_seqlen_q > batch the
+ * decode kernel is not launched at all.  A call whose lengths break this promise
+ * computes only part of the output and sets status bit 4.  Keys at or beyond
+ * seqused_k[b] are never used by the decode kernel, whatever their pages hold;
+ * the prefill kernel multiplies the V rows of masked keys of a partly used tile
+ * by zero, so the cache pages it touches must hold finite values (a cache that
+ * starts zero-filled, as the reference's does, always qualifies).
+ * workspace: see cwm_paged_attn_workspace_zero_bytes for its one requirement. */
 CWM_API int cwm_paged_attn_fwd(const void* q, const void* k, const void* v, void* out,
                        float* lse /* nullable */, const int32_t* cu_seqlens_q,
                        const int32_t* seqused_k, const int32_t* block_table, int batch,
@@ -138,17 +170,20 @@ CWM_API int cwm_paged_attn_fwd(const void* q, const void* k, const void* v, void
  * set of buffers, a serving loop whose memory plan is frozen, a thread that must
  * not touch the allocator.  Arguments are those of cwm_paged_attn_fwd with
  * total_q == batch and max_seqlen_q == 1 (cu_seqlens_q is 0, 1, ..., batch); the
- * split-KV scratch is a fixed array of about 2.6 MB inside the library image,
+ * split-KV scratch is a fixed array of about 2.7 MB inside the library image,
  * which every GPU that loads the library holds until the process exits.
  *
- * Limits: batch <= CWM_NOALLOC_MAX_BATCH, otherwise CWM_ERR_WORKSPACE.  The call
- * performs no cudaMalloc/cudaFree and calls no allocating library routine.  The
+ * Limits: batch <= CWM_NOALLOC_MAX_BATCH and hkv <= 16, otherwise
+ * CWM_ERR_WORKSPACE.  The call performs no cudaMalloc/cudaFree and calls no
+ * allocating library routine; it clears the few KB of the array that must start
+ * at zero with a memset on the caller's stream.  The
  * first call on each device looks up the address of the array (and, like any
  * first launch, lets the CUDA runtime load the kernels), so make that first
  * call before starting a stream capture.  All calls on a device share the one
  * array: two calls that can overlap on the GPU (different streams without an
  * ordering between them) race and give wrong results; calls on one stream are
- * safe.  The array keeps the previous call's contents, which no call relies on. */
+ * safe.  The array keeps the previous call's contents, which no call relies on
+ * (the part that must be zero is cleared by every call). */
 CWM_API int cwm_paged_attn_decode_noalloc(const void* q, const void* k, const void* v, void* out,
                                           float* lse /* nullable */, const int32_t* cu_seqlens_q,
                                           const int32_t* seqused_k, const int32_t* block_table,

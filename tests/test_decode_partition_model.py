@@ -2,8 +2,9 @@
 flat list of 64-token tiles of all (sequence, KV head) segments is cut evenly over
 the persistent CTAs; a segment that lies inside one CTA is written directly, any
 other leaves one partial per CTA in slot 0 (segment began at or before the CTA's
-range) or slot 1 (began inside it), and the combine step reads exactly those slots.
-This restates the index arithmetic in Python and checks its invariants on random
+range) or slot 1 (began inside it) and counts one arrival for the segment; the CTA
+whose arrival is number ``c_last - c_first`` (counting from 0) merges exactly those
+slots in CTA order.  This restates the index arithmetic in Python and checks its invariants on random
 lengths; it guards the rule, not the CUDA code itself (the GPU tests do that)."""
 
 from __future__ import annotations
@@ -40,6 +41,7 @@ def partition(seg_tiles: list[int], grid: int):
 
 
 def combine_reads(seg_tiles, grid, per, starts):
+    """Slots the merging CTA of each split segment reads (CTAs c_first .. c_last)."""
     reads = set()
     for seg, n in enumerate(seg_tiles):
         if n == 0:
@@ -69,6 +71,12 @@ def test_partition_invariants_on_random_lengths():
         # the combine step reads exactly the partials that were written
         if per:
             assert combine_reads(seg_tiles, grid, per, starts) == partials
+        # arrivals per split segment = number of CTAs the merge expects (c_last - c_first + 1)
+        if per:
+            for seg in split:
+                s0, s1 = starts[seg], starts[seg] + seg_tiles[seg]
+                arrivals = sum(1 for _, _, sg in partials if sg == seg)
+                assert arrivals == (s1 - 1) // per - s0 // per + 1
         # at most two partials per CTA (its first and its last segment)
         for cta in range(grid):
             assert sum(1 for c, _, _ in partials if c == cta) <= 2

@@ -150,3 +150,63 @@ def test_prefill_config3_full_size_chunk(ops):
             torch.tensor([0, 64], dtype=torch.int32), torch.tensor([kv_lens[b]], dtype=torch.int32),
             torch.arange(npg, dtype=torch.int32)[None], D**-0.5, window_left)
         assert (o4[b, -64:].cpu().float() - want).abs().max().item() <= 2e-2
+
+
+def test_mixed_config4_full_size(ops):
+    """Config 4 in one varlen call: 16 prefill sequences of 2048 new tokens (no cached
+    prefix) and 240 single-token decodes with contexts lognormal (median 6000, sigma
+    1, clipped to [256, 65536]); global layer and window 8192.  The oracle checks the
+    shortest, the median and the longest decode sequence and the last 64 query rows of
+    two prefill sequences; RMSNorm over [33008, 6144] is checked on sampled rows."""
+    from oracle import ref_rmsnorm
+
+    g = torch.Generator().manual_seed(1004)
+    z = torch.randn(240, generator=g)
+    dec = [int(min(65536, max(256, round(6000 * math.exp(v))))) for v in z.tolist()]
+    q_lens = [2048] * 16 + [1] * 240
+    kv_lens = [2048] * 16 + dec
+    table, n_pages, pages = _tables(kv_lens, g)
+    gd = torch.Generator(device=DEV).manual_seed(11)
+    cache = torch.empty(n_pages * PAGE, 2 * HKV * D, device=DEV, dtype=torch.bfloat16)
+    for r0 in range(0, cache.shape[0], 1 << 16):
+        blk = cache[r0 : r0 + (1 << 16)]
+        blk.copy_(torch.randn(blk.shape, generator=gd, device=DEV))
+    t = sum(q_lens)
+    q = torch.randn(t, HQ, D, generator=gd, device=DEV).to(torch.bfloat16)
+    cu_list = [0]
+    for n in q_lens:
+        cu_list.append(cu_list[-1] + n)
+    cu = torch.tensor(cu_list, dtype=torch.int32, device=DEV)
+    seqk = torch.tensor(kv_lens, dtype=torch.int32, device=DEV)
+    table_d = table.to(DEV)
+    order = sorted(range(16, 256), key=lambda b: kv_lens[b])
+    assert kv_lens[order[-1]] == 65536 or kv_lens[order[-1]] > 40000
+    sampled = [(order[0], 1), (order[120], 1), (order[-1], 1), (3, 64), (15, 64)]
+    for window_left in (-1, 8191):
+        out = _attend(ops, q, cache, cu, seqk, table_d, 2048, window_left)
+        torch.cuda.synchronize()
+        from cwm_b200 import _lib
+        assert _lib.device_status(torch.cuda.current_stream().cuda_stream) == 0
+        for b, rows_checked in sampled:
+            npg = pages[b]
+            rows = torch.cat([cache[int(pg) * PAGE : (int(pg) + 1) * PAGE]
+                              for pg in table[b, :npg]]).cpu()
+            k, v = torch.split(rows, [HKV * D, HKV * D], dim=1)
+            q_rows = q[cu_list[b + 1] - rows_checked : cu_list[b + 1]].cpu()
+            want, _ = ref_paged_gqa_attention(
+                q_rows, k.reshape(-1, PAGE, HKV, D), v.reshape(-1, PAGE, HKV, D),
+                torch.tensor([0, rows_checked], dtype=torch.int32),
+                torch.tensor([kv_lens[b]], dtype=torch.int32),
+                torch.arange(npg, dtype=torch.int32)[None], D**-0.5, window_left)
+            got = out[cu_list[b + 1] - rows_checked : cu_list[b + 1]].cpu().float()
+            assert (got - want).abs().max().item() <= 2e-2, (b, window_left)
+    del cache, q, out
+    # the normalisation that precedes the layer output in config 4
+    x = torch.randn(33008, 6144, generator=gd, device=DEV).to(torch.bfloat16)
+    w = torch.randn(6144, generator=gd, device=DEV).to(torch.bfloat16)
+    y = ops.rmsnorm(x, w, 1e-5)
+    rows = [0, 1, 4095, 16384, 33006, 33007]
+    want = ref_rmsnorm(x[rows].cpu(), w.cpu(), 1e-5)
+    assert (y[rows].cpu().float() - want).abs().max().item() <= 2e-2
+    # and every row is finite and of the right scale
+    assert torch.isfinite(y).all().item()
