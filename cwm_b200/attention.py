@@ -20,13 +20,10 @@ _WS_BATCH_X_HEADS = 16384 * 8
 
 
 def _new_workspace(device: torch.device, batch: int, hkv: int) -> torch.Tensor:
-    lib = _lib.load()
-    need = lib.cwm_paged_attn_workspace_bytes(batch, 0, 0, hkv, 0)
-    ws = torch.empty(need, dtype=torch.uint8, device=device)
-    # the arrival counters at the head of the workspace start at zero; every
-    # call leaves them zero, so this happens once per buffer
-    ws[: lib.cwm_paged_attn_workspace_zero_bytes(batch, hkv)].zero_()
-    return ws
+    need = _lib.load().cwm_paged_attn_workspace_bytes(batch, 0, 0, hkv, 0)
+    # zero-filled once: the arrival counters in it must start at zero, and every
+    # call leaves them zero
+    return torch.zeros(need, dtype=torch.uint8, device=device)
 
 
 def workspace_for(device: torch.device, batch: int, hkv: int = 8) -> torch.Tensor:

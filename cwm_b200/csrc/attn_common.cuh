@@ -41,17 +41,19 @@ struct AttnArgs {
 };
 using DecodeArgs = AttnArgs;
 
-// Split-KV workspace: arrival counters (one per sequence and KV head) followed by two
-// partial states per CTA.  The counters must be zero when a launch starts; every
-// launch leaves them zero again.
+// Split-KV workspace: two partial states per CTA (a size that depends on max_ctas
+// only) followed by the arrival counters (one per sequence and KV head).  The
+// counters must be zero when a launch starts; every launch leaves them zero again.
 size_t decode_workspace_bytes(int batch, int hkv);
 // max_ctas caps the persistent grid (the workspace holds two partials per CTA).
 int launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, AttnArgs a, bool bf16,
                   void* workspace, cudaStream_t stream, int max_ctas = kMaxDecodeCtas);
 // Workspace bytes for a decode grid of at most max_ctas CTAs.
 size_t decode_workspace_bytes_for(int batch, int hkv, int max_ctas);
-// Bytes at the start of the workspace that hold the arrival counters.
+// Bytes of the arrival counters, which start decode_partial_bytes(max_ctas) into the
+// workspace.
 size_t decode_counter_bytes(int batch, int hkv);
+size_t decode_partial_bytes(int max_ctas);
 // Values of the self-test hooks (cwm_test_hooks) for the next launches.
 long long hook_wait_cycles();
 int hook_drop_last_tile();

@@ -519,9 +519,12 @@ size_t decode_counter_bytes(int batch, int hkv) {
   return (static_cast<size_t>(batch) * static_cast<size_t>(hkv) * sizeof(int) + 255) / 256 * 256;
 }
 
+size_t decode_partial_bytes(int max_ctas) {
+  return static_cast<size_t>(max_ctas) * 2 * kPartialFloats * sizeof(float);
+}
+
 size_t decode_workspace_bytes_for(int batch, int hkv, int max_ctas) {
-  return decode_counter_bytes(batch, hkv) +
-         static_cast<size_t>(max_ctas) * 2 * kPartialFloats * sizeof(float);
+  return decode_partial_bytes(max_ctas) + decode_counter_bytes(batch, hkv);
 }
 
 size_t decode_workspace_bytes(int batch, int hkv) {
@@ -530,9 +533,12 @@ size_t decode_workspace_bytes(int batch, int hkv) {
 
 int launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, DecodeArgs a, bool bf16,
                   void* workspace, cudaStream_t stream, int max_ctas) {
-  a.counters = static_cast<int*>(workspace);
-  a.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) +
-                                       decode_counter_bytes(a.batch, a.hkv));
+  // The partial states come first and their size does not depend on the batch, so
+  // the counters sit at the same place for every call that shares the workspace
+  // (a later, larger batch never finds an earlier call's partials under them).
+  a.partial = static_cast<float*>(workspace);
+  a.counters = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) +
+                                      decode_partial_bytes(max_ctas));
   a.wait_cycles = hook_wait_cycles();
   a.test_drop_last = hook_drop_last_tile();
   const size_t smem = decode_smem_bytes(a.batch);

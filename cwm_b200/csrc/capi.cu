@@ -195,10 +195,6 @@ extern "C" size_t cwm_paged_attn_workspace_bytes(int batch, int64_t total_q, int
   return decode_workspace_bytes(batch < 0 ? 0 : batch, hkv > 0 ? hkv : 1);
 }
 
-extern "C" size_t cwm_paged_attn_workspace_zero_bytes(int batch, int hkv) {
-  return decode_counter_bytes(batch < 0 ? 0 : batch, hkv > 0 ? hkv : 1);
-}
-
 extern "C" int cwm_paged_attn_fwd(const void* q, const void* k, const void* v, void* out,
                                   float* lse, const int32_t* cu_seqlens_q,
                                   const int32_t* seqused_k, const int32_t* block_table, int batch,
@@ -334,8 +330,8 @@ constexpr int kNoAllocMaxBatch = CWM_NOALLOC_MAX_BATCH;
 constexpr int kNoAllocMaxKvHeads = 16;
 constexpr int kNoAllocMaxCtas = 304;
 constexpr size_t kNoAllocScratchBytes =
-    static_cast<size_t>(kNoAllocMaxBatch) * kNoAllocMaxKvHeads * sizeof(int) +
-    static_cast<size_t>(kNoAllocMaxCtas) * 2 * 34 * 32 * sizeof(float);
+    static_cast<size_t>(kNoAllocMaxCtas) * 2 * 34 * 32 * sizeof(float) +
+    static_cast<size_t>(kNoAllocMaxBatch) * kNoAllocMaxKvHeads * sizeof(int);
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
 // Device address of the scratch array on the current device.  In host code the
@@ -450,13 +446,14 @@ extern "C" int cwm_paged_attn_decode_noalloc(const void* q, const void* k, const
   a.window_left = window_left;
   a.status = status;
   a.decode_launched = 1;
-  // The arrival counters at the head of the scratch must be zero when the kernel
+  // The arrival counters (behind the partial states) must be zero when the kernel
   // starts.  A launch that ran to its end leaves them zero, but the array is shared
   // by every caller on this device and outlives failed launches, so they are cleared
   // here on the caller's stream (a memset node, not an allocation).  The partial
-  // states behind them need no clearing: a launch reads only slots it wrote itself.
-  CWM_CUDA_CHECK(cudaMemsetAsync(scratch, 0, decode_counter_bytes(batch, hkv),
-                                 static_cast<cudaStream_t>(stream)));
+  // states need no clearing: a launch reads only slots it wrote itself.
+  CWM_CUDA_CHECK(cudaMemsetAsync(
+      static_cast<unsigned char*>(scratch) + decode_partial_bytes(kNoAllocMaxCtas), 0,
+      decode_counter_bytes(batch, hkv), static_cast<cudaStream_t>(stream)));
   return launch_decode(kmap, vmap, a, dtype == CWM_BF16, scratch,
                        static_cast<cudaStream_t>(stream), kNoAllocMaxCtas);
 }

@@ -99,18 +99,15 @@ CWM_API int cwm_rope_kv_write(void* xq, void* xk, const void* xv, void* cache_k,
                       int64_t page_tbl_cols, int64_t cache_stride, int64_t cache_rows,
                       void* stream);
 
-/* Bytes of scratch that cwm_paged_attn_fwd needs for this problem size (arrival
- * counters and split-KV partial results of the decode kernel).  Depends on static
- * sizes only; grows with batch * hkv. */
+/* Bytes of scratch that cwm_paged_attn_fwd needs for this problem size (split-KV
+ * partial results and arrival counters of the decode kernel).  Depends on static
+ * sizes only; grows with batch * hkv.  The workspace must be zero-filled once after
+ * it is allocated.  Every call that completes leaves the part that matters (the
+ * counters) zero again, so one workspace can serve later calls of any batch size
+ * up to the one it was sized for (on one stream, or otherwise ordered) and
+ * CUDA-graph replays, without clearing.  Zero-fill it again after a call for which
+ * cwm_device_status reported bit 2. */
 CWM_API size_t cwm_paged_attn_workspace_bytes(int batch, int64_t total_q, int hq, int hkv, int d);
-
-/* The first cwm_paged_attn_workspace_zero_bytes(batch, hkv) bytes of a workspace
- * (the arrival counters) must be zero when cwm_paged_attn_fwd is first given it:
- * clear them once after allocating.  Every call that completes leaves them zero,
- * so a workspace can be reused by later calls (on one stream, or otherwise ordered)
- * and by CUDA-graph replays without clearing.  Clear them again after a call for
- * which cwm_device_status reported bit 2. */
-CWM_API size_t cwm_paged_attn_workspace_zero_bytes(int batch, int hkv);
 
 /* Self-test hooks (process-wide, for the library's own tests; not part of the
  * reference's interface).  wait_limit_cycles: limit of the bounded waits inside the
@@ -152,7 +149,7 @@ CWM_API int cwm_test_hooks(long long wait_limit_cycles, int drop_last_tile);
  * the prefill kernel multiplies the V rows of masked keys of a partly used tile
  * by zero, so the cache pages it touches must hold finite values (a cache that
  * starts zero-filled, as the reference's does, always qualifies).
- * workspace: see cwm_paged_attn_workspace_zero_bytes for its one requirement. */
+ * workspace: see cwm_paged_attn_workspace_bytes for its one requirement. */
 CWM_API int cwm_paged_attn_fwd(const void* q, const void* k, const void* v, void* out,
                        float* lse /* nullable */, const int32_t* cu_seqlens_q,
                        const int32_t* seqused_k, const int32_t* block_table, int batch,
@@ -192,6 +189,31 @@ CWM_API int cwm_paged_attn_decode_noalloc(const void* q, const void* k, const vo
                                           int64_t kv_token_stride, int64_t bt_stride,
                                           int max_seqlen_k, float softmax_scale, int window_left,
                                           void* stream);
+
+/* Token sampling over x[rows, vocab] (fp32, row stride row_stride elements): one
+ * launch does what FastGen._sample does with several torch calls,
+ * cwm/fastgen/generate.py:996-1014 with cwm/fastgen/utils/sampling.py:6-45.
+ *   is_logits != 0: x holds logits and the probabilities are
+ *     softmax(x / temps[row]) (temps null: 1); otherwise x holds probabilities.
+ *   mode 0: greedy, tokens[row] = first index of the row maximum (torch.argmax).
+ *   mode 1: a draw in index order, the distribution of sample(probs)
+ *     (sampling.py:6-18): the first index whose inclusive running sum exceeds
+ *     uniforms[row] * total.
+ *   mode 2: top_p(probs, top_ps) (sampling.py:21-45): entries in descending order
+ *     (equal values by ascending index), those whose exclusive running sum exceeds
+ *     top_ps[row] are dropped (top_ps null or >= 1: none), the rest renormalised,
+ *     and the draw is the first survivor whose inclusive running sum exceeds
+ *     uniforms[row] * (surviving mass).
+ * uniforms[row] in [0, 1) stands in for torch.multinomial's generator, so that the
+ * caller controls the stream of random numbers and every tensor-parallel rank
+ * draws the same token.  probs[row] receives the probability of the drawn token
+ * after renormalisation (1 for mode 0); kept (nullable) the number of surviving
+ * entries.  Sums are kept in 2^-44 fixed point: results do not depend on thread
+ * timing.  vocab <= 131072 for modes 1 and 2. */
+CWM_API int cwm_sample(const float* x, int is_logits, const float* temps /* nullable */,
+                       const float* top_ps /* nullable */, const float* uniforms, int64_t rows,
+                       int64_t vocab, int64_t row_stride, int mode, int64_t* tokens, float* probs,
+                       int32_t* kept /* nullable */, void* stream);
 
 #ifdef __cplusplus
 }

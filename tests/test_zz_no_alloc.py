@@ -47,8 +47,7 @@ def _call_workspace(lib, pg, p, window_left, stream):
     out = torch.zeros_like(pg.q)
     lse = torch.zeros(p.hq, batch, device=pg.q.device)
     need = lib.cwm_paged_attn_workspace_bytes(batch, batch, p.hq, p.hkv, p.d)
-    ws = torch.empty(need, dtype=torch.uint8, device=pg.q.device)
-    ws[: lib.cwm_paged_attn_workspace_zero_bytes(batch, p.hkv)].zero_()
+    ws = torch.zeros(need, dtype=torch.uint8, device=pg.q.device)
     rc = lib.cwm_paged_attn_fwd(
         pg.q.data_ptr(), k4.data_ptr(), v4.data_ptr(), out.data_ptr(), lse.data_ptr(),
         pg.cu_seqlens_q.data_ptr(), pg.seqused_k.data_ptr(), pg.block_table.data_ptr(), batch,
