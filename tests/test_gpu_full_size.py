@@ -207,6 +207,8 @@ def test_mixed_config4_full_size(ops):
     y = ops.rmsnorm(x, w, 1e-5)
     rows = [0, 1, 4095, 16384, 33006, 33007]
     want = ref_rmsnorm(x[rows].cpu(), w.cpu(), 1e-5)
-    assert (y[rows].cpu().float() - want).abs().max().item() <= 2e-2
+    # within one bf16 rounding step of the fp32 value (2e-2 absolute for |y| <= 4)
+    diff = (y[rows].cpu().float() - want).abs()
+    assert bool((diff <= 2e-2 + want.abs() * 2.0**-8).all())
     # and every row is finite and of the right scale
     assert torch.isfinite(y).all().item()

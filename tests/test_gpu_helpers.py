@@ -272,3 +272,73 @@ def test_rope_kv_write_equals_separate_ops(ops, hq, hkv, mode):
     assert torch.equal(cache_a.view(torch.int16), cache_b.view(torch.int16))
     assert cache_b.abs().sum().item() > 0
     assert _status() == 0
+
+
+@pytest.mark.parametrize("hq,hkv", [(48, 8), (6, 1)])
+@pytest.mark.parametrize("mode", ["prefill", "decode"])
+def test_packed_qkv_rope_kv_write_equals_the_split_path(ops, hq, hkv, mode):
+    """The packed form (one stacked q|k|v projection output, rows read in place, queries
+    written to a fresh tensor) must give the queries and cache rows of rope_kv_write on
+    the split tensors, bit for bit, and must leave the packed rows untouched."""
+    from cwm_b200.attention import qkv_rope_kv_write
+
+    g = torch.Generator().manual_seed(100 + hq)
+    d, page, n_pages = 128, 256, 24
+    if mode == "prefill":
+        t, b = 500, 3
+        lane = torch.sort(torch.randint(0, b, (t,), generator=g)).values.to(torch.int32).to(DEV)
+        pos = torch.cat([torch.arange((lane == i).sum().item()) + 41 * i for i in range(b)]).to(torch.int32)
+        bs = None
+    else:
+        t, b = 6, 6
+        lane = None
+        pos = torch.tensor([0, 255, 256, 700, -1, -1], dtype=torch.int32)
+        bs = torch.tensor(4, dtype=torch.int64, device=DEV)
+    tbl = torch.randperm(n_pages, generator=g)[: b * 3].reshape(b, 3).to(torch.int32).to(DEV)
+    width = (hq + 2 * hkv) * d
+    # rows wider than the packed heads: the row stride differs from the row length
+    buf = torch.randn(t, width + 64, generator=g).to(torch.bfloat16).to(DEV)
+    qkv = buf[:, :width]
+    before = qkv.clone()
+    freqs = ref_rope_freqs(d, 1e6).to(DEV)
+    pos_d = pos.to(DEV)
+    cache_a = torch.zeros(n_pages * page, 2 * hkv * d, device=DEV, dtype=torch.bfloat16)
+    cache_b = torch.zeros_like(cache_a)
+
+    xq, xk, xv = (x.contiguous().view(t, -1, d) for x in
+                  torch.split(before, [hq * d, hkv * d, hkv * d], dim=1))
+    ck, cv = torch.split(cache_a, [hkv * d, hkv * d], dim=1)
+    ops.rope_kv_write(xq, xk, xv, ck, cv, pos_d, freqs, tbl, lane, bs, page)
+    ck2, cv2 = torch.split(cache_b, [hkv * d, hkv * d], dim=1)
+    q_out = qkv_rope_kv_write(qkv, hq, hkv, ck2, cv2, pos_d, freqs, tbl, lane, bs, page)
+
+    assert q_out.shape == (t, hq, d) and q_out.is_contiguous()
+    assert torch.equal(q_out.view(torch.int16), xq.view(torch.int16))
+    assert torch.equal(cache_a.view(torch.int16), cache_b.view(torch.int16))
+    assert torch.equal(qkv.view(torch.int16), before.view(torch.int16))
+    assert cache_b.abs().sum().item() > 0
+    assert _status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_silu_mul_equals_the_two_torch_ops(ops, dtype):
+    """F.silu(x1, inplace=True).mul_(x3) of forward.py:776-781 rounds after each
+    of the two steps; the fused kernel rounds the same way."""
+    from cwm_b200.attention import silu_mul
+
+    g = torch.Generator().manual_seed(7)
+    for t, ffn in ((128, 2688), (3, 8), (1000, 512)):
+        x13 = (torch.randn(t, 2 * ffn, generator=g) * 3).to(dtype).to(DEV)
+        x1, x3 = x13.clone().chunk(2, dim=1)
+        want = torch.nn.functional.silu(x1.contiguous(), inplace=True).mul_(x3)
+        got = silu_mul(x13)
+        assert got.shape == (t, ffn)
+        diff = (got.float() - want.float()).abs()
+        # expf and torch's exp may differ in the last bit before the rounding
+        step = want.float().abs() * (2.0**-7 if dtype == torch.bfloat16 else 2.0**-10
+                                     if dtype == torch.float16 else 2.0**-21) + 1e-30
+        assert bool((diff <= step).all())
+        if dtype != torch.float32:
+            assert (diff > 0).float().mean().item() < 0.01
+    with pytest.raises(ValueError):
+        silu_mul(torch.zeros(4, 7, device=DEV, dtype=torch.bfloat16))
