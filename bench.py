@@ -317,7 +317,7 @@ def main() -> None:
     ap.add_argument("--workload", default="decode_global",
                     choices=["decode_global", "decode_local", "small", "prefill", "prefill_local",
                              "prefill_small", "rmsnorm", "rope_kv_write", "mixed", "mixed_local",
-                             "decoder"])
+                             "decoder", "sampling"])
     ap.add_argument("--decoder-batch", type=int, default=128)
     ap.add_argument("--decoder-ctx", type=int, default=16384)
     ap.add_argument("--decoder-layers", type=int, default=64)
@@ -350,6 +350,8 @@ def main() -> None:
         return
     if args.workload in ("rmsnorm", "rope_kv_write"):
         return bench_helpers(args)
+    if args.workload == "sampling":
+        return bench_sampling(args)
     if args.workload.startswith("mixed"):
         return bench_mixed(args, window_left)
 
@@ -817,14 +819,6 @@ def run_prefill(args, window_left: int, steps: int, with_cpu: bool) -> dict:
 
 
 def bench_decoder(args, rank: int, local_rank: int, world: int) -> None:
-    """Config 5: whole decode step of a CWM-32B-shaped decoder (random bf16 weights),
-    tensor-parallel over ``world`` GPUs, batch 128, contexts of 16384 tokens whose
-    K/V are random (the prompts are not prefilled: their pages are filled directly),
-    one CUDA-graph replay per step; tokens/s = batch * steps / time.  Sampling is
-    not part of the step."""
-    import cwm_b200
-    from cwm_b200.decoder import DecoderArgs, DecodeState, ShardedDecoder
-
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     dist = None
@@ -832,6 +826,107 @@ def bench_decoder(args, rank: int, local_rank: int, world: int) -> None:
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=dev)
+    line = run_decoder(args, rank, local_rank, world, dist, steps=args.steps,
+                       with_cpu=not args.no_cpu_baseline)
+    if rank == 0:
+        print(json.dumps(line))
+    _finish(dist)
+
+
+def _gather_cat(t: torch.Tensor, dim: int, world: int, dist) -> torch.Tensor:
+    if dist is None or world == 1:
+        return t
+    parts = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(parts, t.contiguous())
+    return torch.cat(parts, dim=dim)
+
+
+def decoder_parity(margs, rank: int, world: int, dev, dist, ctx: int, collectives: bool) -> dict:
+    """One decode step of a two-layer model with the real layer shapes (and a small
+    vocabulary), tensor-parallel over the same ranks, against the CPU oracle of the
+    unsharded model built from the gathered weights and caches: checks sharding,
+    all-reduces and the attention kernels together at the shapes that are timed."""
+    import dataclasses
+
+    from cwm_b200.decoder import DecodeState, ShardedDecoder
+    from oracle.ref_decoder import ref_decode_step
+
+    small = dataclasses.replace(margs, n_layers=2, vocab_size=8192)
+    shard_of = world if collectives else 1
+    model = ShardedDecoder(small, rank if collectives else 0, shard_of, dev, seed=7)
+    batch = 2
+    cols = (ctx + 2 + PAGE - 1) // PAGE
+    n_pages = batch * cols
+    cache = model.build_cache(n_pages * PAGE)
+    gen = torch.Generator(device=dev).manual_seed(70 + rank)
+    for c in cache.caches:
+        c.copy_(torch.randn(c.shape, generator=gen, device=dev) * 0.5)
+    g = torch.Generator().manual_seed(71)
+    table = torch.randperm(n_pages, generator=g).reshape(batch, cols).to(torch.int32)
+    tokens = torch.randint(0, small.vocab_size, (batch,), generator=g, dtype=torch.int32)
+    seqlen = torch.tensor([ctx + 1, ctx // 3 + 1], dtype=torch.int32)
+    before = [c.clone() for c in cache.caches]
+    state = DecodeState(batch, table.to(dev), PAGE, dev)
+    state.copy_inputs(state.blktbl, tokens.to(dev), seqlen.to(dev))
+    logits = model.decode(state, cache)
+    torch.cuda.synchronize()
+
+    # full (unsharded) weights and cache rows on every rank, the oracle on rank 0
+    hq_l, hkv_l, d = model.shard.n_q, model.shard.n_kv, small.head_dim
+    layers = []
+    for layer in model.layers:
+        wq, wk, wv = model.split_qkv(layer)
+        w1, w3 = layer["w13"].chunk(2, dim=0)
+        layers.append({
+            "wq": _gather_cat(wq, 0, shard_of, dist), "wk": _gather_cat(wk, 0, shard_of, dist),
+            "wv": _gather_cat(wv, 0, shard_of, dist), "wo": _gather_cat(layer["wo"], 1, shard_of, dist),
+            "w13": torch.cat([_gather_cat(w1, 0, shard_of, dist), _gather_cat(w3, 0, shard_of, dist)]),
+            "w2": _gather_cat(layer["w2"], 1, shard_of, dist),
+            "attention_norm": layer["attention_norm"], "ffn_norm": layer["ffn_norm"],
+            "window_left": layer["window_left"],
+        })
+    emb = _gather_cat(model.tok_embeddings, 0, shard_of, dist)
+    out_w = _gather_cat(model.output, 0, shard_of, dist)
+    full_caches = []
+    for c in before:
+        k, v = torch.split(c, [hkv_l * d, hkv_l * d], dim=1)
+        full_caches.append(torch.cat([_gather_cat(k, 1, shard_of, dist),
+                                      _gather_cat(v, 1, shard_of, dist)], dim=1))
+    result = {"max_abs": None}
+    if rank == 0:
+        weights = {
+            "layers": [{k: (v.float().cpu() if torch.is_tensor(v) else v) for k, v in l.items()}
+                       for l in layers],
+            "tok_embeddings": emb.float().cpu(), "output": out_w.float().cpu(),
+            "norm": model.norm.float().cpu(),
+        }
+        want = ref_decode_step(weights, tokens, seqlen, table,
+                               [c.float().cpu() for c in full_caches], model.freqs.cpu(),
+                               small.n_heads, small.n_kv_heads, d, PAGE, small.norm_eps)
+        err = (logits.cpu() - want).abs().max().item()
+        scale = want.abs().max().item()
+        result = {"max_abs": err, "logit_scale": scale, "tolerance": 3e-2 * scale,
+                  "against": "CPU oracle decode step of the unsharded two-layer model (real layer "
+                             f"shapes, vocabulary 8192, contexts {ctx + 1} and {ctx // 3 + 1}) built "
+                             "from the gathered weights and cache rows; logits of rank 0"}
+        if not err <= 3e-2 * scale:
+            raise SystemExit(f"decoder parity check failed: max-abs {err} vs scale {scale}")
+    del model, cache, before, full_caches, layers, emb, out_w
+    torch.cuda.empty_cache()
+    return result
+
+
+def run_decoder(args, rank: int, local_rank: int, world: int, dist, steps: int,
+                with_cpu: bool) -> dict:
+    """Config 5: whole decode step of a CWM-32B-shaped decoder (random bf16 weights),
+    tensor-parallel over ``world`` GPUs, batch 128, contexts of 16384 tokens whose
+    K/V are random (the prompts are not prefilled: their pages are filled directly),
+    one CUDA-graph replay per step; tokens/s = batch * steps / time.  Sampling is
+    not part of the step."""
+    from cwm_b200.decoder import DecoderArgs, DecodeState, ShardedDecoder
+
+    t_setup = time.time()
+    dev = torch.device("cuda", local_rank)
     margs = DecoderArgs(n_layers=args.decoder_layers)
     batch, ctx = args.decoder_batch, args.decoder_ctx
     shard_of = world
@@ -839,7 +934,9 @@ def bench_decoder(args, rank: int, local_rank: int, world: int) -> None:
         if world != 1:
             raise SystemExit("--as-shard needs a single process")
         shard_of = args.as_shard
-    total_steps = max(3, args.warmup) + args.steps + 4
+    parity = decoder_parity(margs, rank, world, dev, dist, min(ctx, 16384),
+                            collectives=shard_of == world)
+    total_steps = max(3, args.warmup) + steps * args.repeats + 4
     cols = (ctx + total_steps + PAGE - 1) // PAGE
     n_pages = batch * cols
     kv_gb = n_pages * PAGE * (HKV // shard_of) * 2 * D * 2 * margs.n_layers / 1e9
@@ -847,7 +944,8 @@ def bench_decoder(args, rank: int, local_rank: int, world: int) -> None:
     if kv_gb + 20 > free_gb:
         raise SystemExit(f"decoder workload needs {kv_gb:.0f} GB of KV cache per GPU, "
                          f"{free_gb:.0f} GB free: use more GPUs or smaller --decoder-* values")
-    model = ShardedDecoder(margs, rank, shard_of, dev, seed=5, collectives=shard_of == world)
+    model = ShardedDecoder(margs, rank if shard_of == world else 0, shard_of, dev, seed=5,
+                           collectives=shard_of == world)
     cache = model.build_cache(n_pages * PAGE)
     cache.caches[0].normal_()
     for c in cache.caches[1:]:
@@ -882,18 +980,22 @@ def bench_decoder(args, rank: int, local_rank: int, world: int) -> None:
     for _ in range(max(3, args.warmup)):
         step()
     sync_all()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    setup_s = time.time() - t_setup
+    runs = []
     with ClockSampler(local_rank) as clocks:
-        sync_all()
-        e0.record()
-        for _ in range(args.steps):
-            step()
-        e1.record()
-        sync_all()
-    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if dist is not None:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_per_step = float(ms.item()) / args.steps
+        for _ in range(args.repeats):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            sync_all()
+            e0.record()
+            for _ in range(steps):
+                step()
+            e1.record()
+            sync_all()
+            ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+            if dist is not None:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            runs.append(float(ms.item()) / steps)
+    ms_per_step, runs = median_and_runs(runs)
     finite = bool(torch.isfinite(logits).all().item())
     peaks, peak_kind = measured_peaks()
     lefts = [l["window_left"] for l in model.layers]
@@ -903,9 +1005,9 @@ def bench_decoder(args, rank: int, local_rank: int, world: int) -> None:
     bound_ms = (kv_bytes + w_bytes) / (peaks["hbm_gbs"] * 1e9) * 1e3
     line = {
         "metric": "decode_tokens_per_s", "value": batch / (ms_per_step * 1e-3), "unit": "tokens/s",
-        "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "n_gpus": world, "steps": steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms_per_step, "ms_per_step_runs": runs, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "config 5: CWM-32B-shaped decoder decode step, random weights",
                    "batch": batch, "context": ctx, "layers": margs.n_layers,
                    "global_layers": sum(1 for v in lefts if v < 0), "parallelism": f"tp{world}",
@@ -913,6 +1015,7 @@ def bench_decoder(args, rank: int, local_rank: int, world: int) -> None:
                       if shard_of != world else {}),
                    "launch": "one CUDA-graph replay per step", "logits_finite": finite,
                    "sampling": "excluded"},
+        "parity": parity, "setup_s": round(setup_s, 1),
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "lower_bound_ms": bound_ms, "frac": bound_ms / ms_per_step,
                      "kv_bytes_per_gpu": kv_bytes, "weight_bytes_per_gpu": w_bytes,
@@ -920,12 +1023,11 @@ def bench_decoder(args, rank: int, local_rank: int, world: int) -> None:
                      "note": "lower bound = (attended KV + weights read once) / HBM peak; "
                              "all-reduce time not included"},
     }
-    if rank == 0:
-        if world == 1 and not args.no_cpu_baseline:  # single-process runs only
-            line["cpu_baseline"] = cpu_decoder_baseline(margs, batch, ctx, args.cpu_seconds)
-        print(json.dumps(line))
-    del graph, logits
-    _finish(dist)
+    if rank == 0 and world == 1 and with_cpu:  # single-process runs only
+        line["cpu_baseline"] = cpu_decoder_baseline(margs, batch, ctx, args.cpu_seconds)
+    del graph, logits, model, cache
+    torch.cuda.empty_cache()
+    return line
 
 
 def _time_steps(step, steps: int, warmup: int) -> float:
@@ -986,6 +1088,66 @@ def bench_helpers(args) -> None:
         "config": {"workload": name, "bytes": nbytes},
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                     "peak_kind": f"of {peak_kind}"},
+    }))
+
+
+def bench_sampling(args) -> None:
+    """Token sampling at the engine's shapes: 128 rows of 128256 fp32 logits,
+    temperature 0.7, top-p 0.95 on every row (descending-order draw) and without
+    top-p (index-order draw); one launch per step.  The algorithmic bytes are one
+    read of the logits; the kernel makes several passes, all but the first served
+    by L2 (65.7 MB fits)."""
+    from cwm_b200 import sampling
+    from oracle.ref_sampling import ref_sample_logits
+
+    dev = torch.device("cuda", 0)
+    rows, vocab = 128, 128256
+    g = torch.Generator().manual_seed(1006)
+    logits_h = torch.randn(rows, vocab, generator=g) * 2.5
+    logits = logits_h.to(dev)
+    temps = torch.full((rows,), 0.7, device=dev)
+    top_ps = torch.full((rows,), 0.95, device=dev)
+    u = torch.rand(rows, generator=g).to(dev)
+    peaks, peak_kind = measured_peaks()
+    nbytes = rows * vocab * 4
+    out = {}
+    for name, tp in (("top_p", top_ps), ("index_order", None)):
+        ms = _time_steps(lambda: sampling.sample_logits(logits, temps, tp, True, uniforms=u),
+                         args.steps, args.warmup)
+        out[name] = {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                     "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    ms = _time_steps(lambda: sampling.sample_logits(logits, temps, None, False), args.steps,
+                     args.warmup)
+    out["greedy"] = {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                     "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    # parity on the timed inputs: the reference's fp32 path on 8 of the rows
+    tok, _ = sampling.sample_logits(logits, temps, top_ps, True, uniforms=u)
+    want, _ = ref_sample_logits(logits_h[:8], temps[:8].cpu(), top_ps[:8].cpu(), True, u[:8].cpu())
+    same = int((tok[:8].cpu() == want).sum())
+    if same < 7:
+        raise SystemExit(f"sampling parity check failed: {same} of 8 tokens agree")
+    torch.set_num_threads(os.cpu_count() or 1)
+    t0 = time.perf_counter()
+    reps = 0
+    while time.perf_counter() - t0 < min(args.cpu_seconds, 10.0):
+        ref_sample_logits(logits_h[:16], temps[:16].cpu(), top_ps[:16].cpu(), True, u[:16].cpu())
+        reps += 1
+    cpu_s = (time.perf_counter() - t0) / reps / 16 * rows
+    print(json.dumps({
+        "metric": "sampling_hbm_gbs", "value": out["top_p"]["gbs"], "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": out["top_p"]["ms"],
+        "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "sampling: 128 x 128256 fp32 logits, temperature 0.7, top-p 0.95",
+                   "bytes": nbytes},
+        "modes": out, "parity": {"tokens_equal_of_8": same},
+        "cpu_baseline": {"value": nbytes / cpu_s / 1e9, "unit": "GB/s",
+                         "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{reps} passes over 16 rows with the torch restatement of the "
+                                   "reference path (softmax, sort, cumsum, mask, draw), scaled to "
+                                   "128 rows"},
+        "roofline": {"bound": "hbm", "achieved": out["top_p"]["gbs"], "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": out["top_p"]["frac"], "traffic": None,
                      "peak_kind": f"of {peak_kind}"},
     }))
 
