@@ -65,8 +65,10 @@ def workspace_for(device: torch.device, batch: int, hkv: int = 8) -> torch.Tenso
 def reset_workspaces() -> None:
     """Clear the arrival counters of every cached workspace (a call that ended with
     a device status word other than 0 may have left them non-zero)."""
-    for ws in list(_workspaces.values()) + list(_capture_workspaces.values()):
-        ws.zero_()
+    # a workspace made inside torch.inference_mode() may only be written in that mode
+    with torch.inference_mode():
+        for ws in list(_workspaces.values()) + list(_capture_workspaces.values()):
+            ws.zero_()
 
 
 _lib.on_bad_status.append(reset_workspaces)

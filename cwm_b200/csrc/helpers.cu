@@ -622,8 +622,58 @@ __global__ void silu_mul_kernel(const uint4* __restrict__ x13, uint4* __restrict
   }
 }
 
+// Copies n blocks of `rows` rows of `row_vecs` 16-byte vectors each; block i goes
+// from src_ptrs[i] to dst_ptrs[i] with the row pitches given.  Either side may be
+// pinned host memory (device-accessible under unified addressing): the copy then
+// crosses the host link as plain 16-byte loads or stores issued by many CTAs.
+// blockIdx.y = block, blockIdx.x strides over the block's vectors.
+__global__ void block_copy_kernel(const unsigned long long* __restrict__ dst_ptrs,
+                                  const unsigned long long* __restrict__ src_ptrs, int rows,
+                                  int row_vecs, long long dst_pitch_vecs,
+                                  long long src_pitch_vecs) {
+  const uint4* src = reinterpret_cast<const uint4*>(src_ptrs[blockIdx.y]);
+  uint4* dst = reinterpret_cast<uint4*>(dst_ptrs[blockIdx.y]);
+  const long long total = static_cast<long long>(rows) * row_vecs;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / row_vecs, c = i - r * row_vecs;
+    dst[r * dst_pitch_vecs + c] = src[r * src_pitch_vecs + c];
+  }
+}
+
 }  // namespace
 }  // namespace cwm
+
+extern "C" int cwm_block_copy(const uint64_t* dst_ptrs, const uint64_t* src_ptrs, int64_t n,
+                              int64_t rows, int64_t row_bytes, int64_t dst_pitch_bytes,
+                              int64_t src_pitch_bytes, void* stream) {
+  if (n == 0 || rows == 0 || row_bytes == 0) return CWM_OK;
+  if (!dst_ptrs || !src_ptrs) {
+    set_error("block_copy: null pointer");
+    return CWM_ERR_INVALID;
+  }
+  if (n < 0 || rows < 0 || row_bytes < 0 || dst_pitch_bytes < row_bytes ||
+      src_pitch_bytes < row_bytes || n > 65535 || rows > 0x7fffffff) {
+    set_error("block_copy: bad size argument (at most 65535 blocks per call)");
+    return CWM_ERR_INVALID;
+  }
+  if (row_bytes % 16 != 0 || dst_pitch_bytes % 16 != 0 || src_pitch_bytes % 16 != 0) {
+    set_error("block_copy: rows and pitches must be multiples of 16 bytes");
+    return CWM_ERR_UNSUPPORTED;
+  }
+  const long long vecs = rows * (row_bytes / 16);
+  const int threads = 256;
+  long long gx = (vecs + threads * 8 - 1) / (threads * 8);  // about 8 vectors per thread
+  if (gx < 1) gx = 1;
+  if (gx > 64) gx = 64;
+  dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(n), 1);
+  block_copy_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const unsigned long long*>(dst_ptrs),
+      reinterpret_cast<const unsigned long long*>(src_ptrs), static_cast<int>(rows),
+      static_cast<int>(row_bytes / 16), dst_pitch_bytes / 16, src_pitch_bytes / 16);
+  CWM_CUDA_CHECK(cudaGetLastError());
+  return CWM_OK;
+}
 
 extern "C" int cwm_rope_kv_write(void* xq, void* xk, const void* xv, void* cache_k, void* cache_v,
                                  const int32_t* pos, const float* freqs, const int32_t* page_tbl,

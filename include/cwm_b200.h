@@ -210,6 +210,18 @@ CWM_API int cwm_paged_attn_decode_noalloc(const void* q, const void* k, const vo
                                           int max_seqlen_k, float softmax_scale, int window_left,
                                           void* stream);
 
+/* Copies n cache blocks in one launch: block i is `rows` rows of row_bytes bytes, read
+ * from src_ptrs[i] with row pitch src_pitch_bytes and written to dst_ptrs[i] with row
+ * pitch dst_pitch_bytes.  dst_ptrs / src_ptrs are device-readable arrays of
+ * addresses; the addresses may point into device memory or into pinned host memory
+ * (the copy then runs over the host link without a copy-engine call per block).
+ * Replaces the per-lane, per-block copy_ loops of DynCache.page_in / page_out,
+ * cwm/fastgen/utils/cache.py:227-235 and :251-257.  Rows and pitches in multiples of
+ * 16 bytes, 16-byte aligned addresses, n <= 65535. */
+CWM_API int cwm_block_copy(const uint64_t* dst_ptrs, const uint64_t* src_ptrs, int64_t n,
+                           int64_t rows, int64_t row_bytes, int64_t dst_pitch_bytes,
+                           int64_t src_pitch_bytes, void* stream);
+
 /* Token sampling over x[rows, vocab] (fp32, row stride row_stride elements): one
  * launch does what FastGen._sample does with several torch calls,
  * cwm/fastgen/generate.py:996-1014 with cwm/fastgen/utils/sampling.py:6-45.
