@@ -169,7 +169,7 @@ class DynCache(ModelCache):
 
     def cache_kv(self, n: int) -> tuple[torch.Tensor, ...]:
         if not self.host_cache.disabled and (self.mode & 1):
-            assert self.h2d_events and self.h2d_events[0][1] == n, \\
+            assert self.h2d_events and self.h2d_events[0][1] == n, \
                 f"sync event is not available for layer {n}"
             ev, _ = self.h2d_events.pop(0)
             ev.wait()  # the page-in of this layer is done before it is read
