@@ -55,6 +55,12 @@ SIGNATURES: dict[str, tuple] = {
     "cwm_block_copy": (
         c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p],
     ),
+    "cwm_allreduce": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p],
+    ),
+    "cwm_allreduce_flag_ints": (c_int, []),
+    "cwm_allreduce_ctas": (c_int, [c_int64, c_int]),
     "cwm_silu_mul": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "cwm_paged_attn_workspace_bytes": (c_size_t, [c_int, c_int64, c_int, c_int, c_int]),
     "cwm_test_hooks": (c_int, [ctypes.c_longlong, c_int]),

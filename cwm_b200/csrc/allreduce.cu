@@ -1,0 +1,221 @@
+// Sum all-reduce of a small activation tensor over the GPUs of one node, as one
+// kernel over peer memory (NVLink / NVSwitch loads and stores), for the
+// row-parallel products of a tensor-parallel decoder layer.
+//
+// The reference engine sends these messages (batch x 6144 bf16 = 1.5 MB in decode)
+// through a custom one-shot all-reduce below 8 MiB and through NCCL otherwise
+// (cwm/fastgen/utils/collectives.py:28-45,73-88).  At this size the cost is
+// latency: a two-shot exchange moves 2 * (world - 1) / world of the message per GPU
+// and needs two rounds of flags.
+//
+// Every rank owns three buffers that all ranks can address: `in` (the GEMM writes
+// its output there), `red` (this rank's reduced slice) and a small array of flags.
+// One launch on every rank:
+//   1. flag round 0: "my input is complete" (the launch is behind the GEMM in the
+//      stream) to every peer, wait for the same from every peer;
+//   2. reduce-scatter: rank r sums slice r of all ranks' `in` in rank order with
+//      fp32 accumulation (every rank later copies the same rounded values, so all
+//      ranks end with identical results) into its `red`;
+//   3. flag round 1: "my slice is reduced";
+//   4. all-gather: copy every rank's `red` slice into the local output.
+// Flags carry an epoch that each launch advances, so nothing is ever reset and the
+// launch can be replayed from a CUDA graph.  Each CTA synchronises with the CTA of
+// the same index on the other ranks only, through its own flag slots.  Every wait
+// is bounded; a wait that runs out sets status bit 2 and the kernel returns.
+#include <string.h>
+
+#include "common.cuh"
+
+namespace cwm {
+namespace {
+
+constexpr int kArThreads = 256;
+constexpr int kArMaxCtas = 64;
+constexpr int kArMaxWorld = 8;
+constexpr long long kArSpinLimit = 1ll << 24;  // polls of a flag before giving up
+
+struct ArArgs {
+  const uint4* in[kArMaxWorld];   // every rank's input buffer
+  const uint4* red[kArMaxWorld];  // every rank's reduced-slice buffer
+  int* flags[kArMaxWorld];        // every rank's flags: [2 rounds][kArMaxCtas][kArMaxWorld]
+  uint4* out;                     // local result
+  int* epoch;                     // local: [0] epoch of this launch, [1] CTAs finished
+  int* status;
+  long long slice_vecs;  // 16-byte vectors per rank's slice
+  int rank;
+  int world;
+};
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// All ranks' CTAs of this index meet: thread t < world tells rank t and then waits
+// for rank t's word.  Returns false (for the whole CTA) when a wait ran out.
+__device__ __forceinline__ bool flag_round(const ArArgs& a, int round, int epoch) {
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();  // also: every thread's earlier writes precede the release below
+  if (threadIdx.x < a.world) {
+    const int peer = threadIdx.x;
+    const int slot = (round * kArMaxCtas + blockIdx.x) * kArMaxWorld;
+    st_release_sys(a.flags[peer] + slot + a.rank, epoch);
+    const int* mine = a.flags[a.rank] + slot + peer;
+    long long polls = 0;
+    while (ld_acquire_sys(mine) != epoch) {
+      if (++polls > kArSpinLimit) {
+        failed = 1;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return failed == 0;
+}
+
+template <bool kBf16>
+__device__ __forceinline__ void accumulate(float (&acc)[8], uint4 v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if constexpr (kBf16) {
+      acc[2 * i] += __uint_as_float(w[i] << 16);
+      acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+    } else {
+      const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+      acc[2 * i] += __low2float(h);
+      acc[2 * i + 1] += __high2float(h);
+    }
+  }
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArArgs a) {
+  const int epoch = *a.epoch;
+  bool ok = flag_round(a, 0, epoch);
+  // ---- reduce-scatter: my slice of everybody's input, summed in rank order
+  if (ok) {
+    const long long base = static_cast<long long>(a.rank) * a.slice_vecs;
+    uint4* my_red = const_cast<uint4*>(a.red[a.rank]);
+    for (long long i = static_cast<long long>(blockIdx.x) * kArThreads + threadIdx.x;
+         i < a.slice_vecs; i += static_cast<long long>(gridDim.x) * kArThreads) {
+      uint4 v[kArMaxWorld];
+#pragma unroll
+      for (int p = 0; p < kArMaxWorld; ++p) {
+        if (p < a.world) v[p] = a.in[p][base + i];
+      }
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int p = 0; p < kArMaxWorld; ++p) {
+        if (p < a.world) accumulate<kBf16>(acc, v[p]);
+      }
+      uint4 r;
+      r.x = pack2<kBf16>(acc[0], acc[1]);
+      r.y = pack2<kBf16>(acc[2], acc[3]);
+      r.z = pack2<kBf16>(acc[4], acc[5]);
+      r.w = pack2<kBf16>(acc[6], acc[7]);
+      my_red[i] = r;
+    }
+    __threadfence_system();
+    ok = flag_round(a, 1, epoch);
+  }
+  // ---- all-gather: every rank's reduced slice into the local output
+  if (ok) {
+    for (int p = 0; p < a.world; ++p) {
+      const int src = (a.rank + p) % a.world;  // start with the local slice, spread the peers
+      const uint4* from = a.red[src];
+      uint4* to = a.out + static_cast<long long>(src) * a.slice_vecs;
+      for (long long i = static_cast<long long>(blockIdx.x) * kArThreads + threadIdx.x;
+           i < a.slice_vecs; i += static_cast<long long>(gridDim.x) * kArThreads) {
+        to[i] = from[i];
+      }
+    }
+  } else if (threadIdx.x == 0) {
+    atomicOr(a.status, DEV_WAIT_TIMEOUT);
+  }
+  // ---- the last CTA to finish advances the epoch for the next launch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int done = atomicAdd(a.epoch + 1, 1);
+    if (done == static_cast<int>(gridDim.x) - 1) {
+      a.epoch[1] = 0;
+      a.epoch[0] = epoch + 1;
+    }
+  }
+}
+
+}  // namespace
+}  // namespace cwm
+
+using namespace cwm;
+
+extern "C" int cwm_allreduce_ctas(int64_t n_elems, int world) {
+  if (n_elems <= 0 || world <= 0) return 0;
+  const long long slice_vecs = n_elems / 8 / world;
+  long long ctas = (slice_vecs + kArThreads - 1) / kArThreads;
+  if (ctas < 1) ctas = 1;
+  if (ctas > kArMaxCtas) ctas = kArMaxCtas;
+  return static_cast<int>(ctas);
+}
+
+extern "C" int cwm_allreduce_flag_ints(void) { return 2 * kArMaxCtas * kArMaxWorld; }
+
+extern "C" int cwm_allreduce(const uint64_t* in_ptrs, const uint64_t* red_ptrs,
+                             const uint64_t* flag_ptrs, void* out, int32_t* epoch,
+                             int64_t n_elems, int dtype, int rank, int world, void* stream) {
+  if (n_elems == 0) return CWM_OK;
+  if (!in_ptrs || !red_ptrs || !flag_ptrs || !out || !epoch) {
+    set_error("allreduce: null pointer");
+    return CWM_ERR_INVALID;
+  }
+  if (world < 1 || world > kArMaxWorld || rank < 0 || rank >= world || n_elems < 0) {
+    set_error("allreduce: bad rank / world (at most %d ranks)", kArMaxWorld);
+    return CWM_ERR_INVALID;
+  }
+  if (dtype != CWM_BF16 && dtype != CWM_F16) {
+    set_error("allreduce: bf16 and fp16 only");
+    return CWM_ERR_UNSUPPORTED;
+  }
+  if (n_elems % (8ll * world) != 0) {
+    set_error("allreduce: %lld elements do not split into 16-byte vectors over %d ranks",
+              static_cast<long long>(n_elems), world);
+    return CWM_ERR_UNSUPPORTED;
+  }
+  ArArgs a;
+  memset(&a, 0, sizeof(a));
+  for (int p = 0; p < world; ++p) {
+    if (in_ptrs[p] % 16 || red_ptrs[p] % 16 || flag_ptrs[p] % 4 || !in_ptrs[p] || !red_ptrs[p] ||
+        !flag_ptrs[p]) {
+      set_error("allreduce: peer buffer %d is null or misaligned", p);
+      return CWM_ERR_INVALID;
+    }
+    a.in[p] = reinterpret_cast<const uint4*>(in_ptrs[p]);
+    a.red[p] = reinterpret_cast<const uint4*>(red_ptrs[p]);
+    a.flags[p] = reinterpret_cast<int*>(flag_ptrs[p]);
+  }
+  a.out = static_cast<uint4*>(out);
+  a.epoch = epoch;
+  a.status = status_word();
+  if (a.status == nullptr) {
+    set_error("allreduce: cannot resolve the device status word");
+    return CWM_ERR_CUDA;
+  }
+  a.slice_vecs = n_elems / 8 / world;
+  a.rank = rank;
+  a.world = world;
+  const int ctas = cwm_allreduce_ctas(n_elems, world);
+  auto st = static_cast<cudaStream_t>(stream);
+  if (dtype == CWM_BF16) {
+    allreduce_kernel<true><<<ctas, kArThreads, 0, st>>>(a);
+  } else {
+    allreduce_kernel<false><<<ctas, kArThreads, 0, st>>>(a);
+  }
+  CWM_CUDA_CHECK(cudaGetLastError());
+  return CWM_OK;
+}

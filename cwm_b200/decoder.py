@@ -95,17 +95,25 @@ class ShardedDecoder:
 
     def __init__(self, args: DecoderArgs, rank: int, world: int, device: torch.device,
                  dtype: torch.dtype = torch.bfloat16, seed: int = 0, std: float = 0.02,
-                 group: dist.ProcessGroup | None = None, collectives: bool = True) -> None:
+                 group: dist.ProcessGroup | None = None, collectives: bool = True,
+                 peer_all_reduce: bool = False) -> None:
         """``collectives=False`` builds the shard of ``rank`` without a process group
         and skips the all-reduces and the logits gather: the per-GPU work of a
-        ``world``-way run on a single GPU, for profiling."""
+        ``world``-way run on a single GPU, for profiling.  ``peer_all_reduce`` sends
+        the row-parallel sums through this package's peer-memory kernel instead of
+        the process group's all-reduce (all ranks on one node)."""
         if args.ffn_dim % world or args.vocab_size % world:
             raise ValueError("ffn_dim and vocab_size must be divisible by the group size")
         self.args = args
         self.rank, self.world = rank, world
         self.device, self.dtype = device, dtype
         self.shard: HeadShard = shard_heads(rank, world, args.n_heads, args.n_kv_heads)
-        self.coll = Collectives(group) if world > 1 and collectives else None
+        self.coll = None
+        if world > 1 and collectives:
+            from .tp import PeerAllReduce
+
+            peer = PeerAllReduce(group, device) if peer_all_reduce else None
+            self.coll = Collectives(group, peer)
         gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
 
         def w(*shape: int) -> torch.Tensor:
@@ -144,6 +152,11 @@ class ShardedDecoder:
     def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         return x if self.coll is None else self.coll.all_reduce(x)
 
+    def _linear_all_reduce(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        if self.coll is None:
+            return F.linear(x, weight)
+        return self.coll.linear_all_reduce(x, weight)
+
     def _embed(self, tokens: torch.Tensor) -> torch.Tensor:
         """Vocabulary-parallel embedding, ``forward.py:134-167``."""
         local = self.tok_embeddings.shape[0]
@@ -174,9 +187,9 @@ class ShardedDecoder:
             qkv = F.linear(x, layer["wqkv"])
             attn = gqa_attention_packed(qkv, hq, hkv, cache, i, bias, q_seqpos, q_batch,
                                         actual_batch_size, self.freqs, layer["window_left"])
-            h_out = self._all_reduce(F.linear(attn.flatten(1, 2), layer["wo"]))
+            h_out = self._linear_all_reduce(attn.flatten(1, 2), layer["wo"])
             x = add_rmsnorm(h, h_out, layer["ffn_norm"], a.norm_eps)
-            h_out = self._all_reduce(F.linear(silu_mul(F.linear(x, layer["w13"])), layer["w2"]))
+            h_out = self._linear_all_reduce(silu_mul(F.linear(x, layer["w13"])), layer["w2"])
             next_norm = self.layers[i + 1]["attention_norm"] if i + 1 < n_layers else self.norm
             x = add_rmsnorm(h, h_out, next_norm, a.norm_eps)
         if logits_idx is not None:

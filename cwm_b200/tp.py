@@ -65,18 +65,141 @@ def shard_cache_rows(full_rows: torch.Tensor, shard: HeadShard, n_kv_heads: int,
     return torch.cat([k[:, sl], v[:, sl]], dim=1).contiguous()
 
 
+class PeerAllReduce:
+    """The node-local all-reduce kernel of this package (``cwm_allreduce``) with its
+    buffers: the counterpart of the reference's ``CustomAllreduce``
+    (``cwm/fastgen/utils/collectives.py:11-15,39-45``).
+
+    Each rank allocates an input buffer, a scratch buffer for its reduced slice and
+    a flag array, and maps the other ranks' three buffers through CUDA IPC (the
+    ranks are processes on one node).  ``input_buffer`` hands out a view of the
+    input buffer for the producer (a GEMM with ``out=``) to write into, so that no
+    copy is needed; ``all_reduce`` takes such a view, or copies any other tensor in.
+    Results are new tensors.  ``close`` drops the mappings; call it on every rank,
+    with a barrier before any rank exits, so that no rank unmaps memory a peer's
+    kernel could still read.
+    """
+
+    def __init__(self, group: dist.ProcessGroup | None, device: torch.device,
+                 max_bytes: int = 8 << 20) -> None:
+        from . import _lib
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("the peer all-reduce serves at most 8 ranks of one node")
+        self.device = device
+        self.max_bytes = max_bytes
+        lib = _lib.load()
+        self._in = torch.zeros(max_bytes, dtype=torch.uint8, device=device)
+        self._red = torch.zeros(max_bytes // self.world + 16, dtype=torch.uint8, device=device)
+        self._flags = torch.zeros(lib.cwm_allreduce_flag_ints(), dtype=torch.int32, device=device)
+        self._epoch = torch.tensor([1, 0], dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        self._mapped: list = []  # keeps the peers' storages mapped
+        self._tables = []
+        for t in (self._in, self._red, self._flags):
+            handle = t.untyped_storage()._share_cuda_()
+            offset = t.storage_offset() * t.element_size()
+            gathered: list = [None] * self.world
+            dist.all_gather_object(gathered, (handle, offset), group=group)
+            ptrs = []
+            for p, (h, off) in enumerate(gathered):
+                if p == self.rank:
+                    ptrs.append(t.data_ptr())
+                    continue
+                storage = torch.UntypedStorage._new_shared_cuda(*h)
+                self._mapped.append(storage)
+                ptrs.append(storage.data_ptr() + off)
+            self._tables.append((ctypes_array(ptrs), ptrs))
+        dist.barrier(group=group)
+
+    def input_buffer(self, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """A view of the shared input buffer with the given shape (one at a time: the
+        next ``input_buffer`` call returns the same memory)."""
+        n = 1
+        for d in shape:
+            n *= d
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        if nbytes > self.max_bytes:
+            raise ValueError(f"{nbytes} bytes exceed the all-reduce buffer of {self.max_bytes}")
+        return self._in[:nbytes].view(dtype).view(shape)
+
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        from . import _lib
+        from .kernels import _DTYPES, _stream
+
+        if x.dtype not in (torch.bfloat16, torch.float16) or not x.is_contiguous():
+            raise ValueError("the peer all-reduce takes contiguous bf16 or fp16 tensors")
+        n = x.numel()
+        if n * x.element_size() > self.max_bytes:
+            raise ValueError("tensor exceeds the all-reduce buffer")
+        if x.data_ptr() != self._in.data_ptr():
+            self.input_buffer(tuple(x.shape), x.dtype).copy_(x)
+        out = torch.empty_like(x)
+        code = _lib.load().cwm_allreduce(
+            self._tables[0][0], self._tables[1][0], self._tables[2][0], out.data_ptr(),
+            self._epoch.data_ptr(), n, _DTYPES[x.dtype], self.rank, self.world, _stream(x))
+        _lib.check(code, "allreduce")
+        return out
+
+    def supports(self, x: torch.Tensor) -> bool:
+        return (x.dtype in (torch.bfloat16, torch.float16) and x.is_contiguous()
+                and x.numel() % (8 * self.world) == 0
+                and x.numel() * x.element_size() <= self.max_bytes)
+
+    def close(self) -> None:
+        self._mapped.clear()
+        self._tables.clear()
+
+
+def ctypes_array(values: list[int]):
+    import ctypes
+
+    return (ctypes.c_uint64 * len(values))(*values)
+
+
 class Collectives:
     """The subset of ``cwm/fastgen/utils/collectives.py`` that the attention path
-    uses: a sum all-reduce over the tensor-parallel group."""
+    uses: a sum all-reduce over the tensor-parallel group, through the node-local
+    peer-memory kernel when ``peer`` is given and the tensor qualifies (the
+    reference's rule: its custom all-reduce below 8 MiB, ``collectives.py:73-88``),
+    through the process group's all-reduce (NCCL on GPUs, gloo in CPU tests)
+    otherwise."""
 
-    def __init__(self, group: dist.ProcessGroup | None = None) -> None:
+    def __init__(self, group: dist.ProcessGroup | None = None,
+                 peer: PeerAllReduce | None = None) -> None:
         self.group = group
         self.tp_size = dist.get_world_size(group)
         self.tp_rank = dist.get_rank(group)
+        self.peer = peer
 
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.peer is not None and self.peer.supports(x):
+            return self.peer.all_reduce(x)
         dist.all_reduce(x, op=dist.ReduceOp.SUM, group=self.group)
         return x
+
+    def linear_all_reduce(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        """``all_reduce(F.linear(x, weight))`` with the product written straight into
+        the shared input buffer when the peer kernel is used."""
+        if self.peer is not None:
+            shape = (*x.shape[:-1], weight.shape[0])
+            n = 1
+            for d in shape:
+                n *= d
+            if (x.dtype in (torch.bfloat16, torch.float16) and n % (8 * self.tp_size) == 0
+                    and n * x.element_size() <= self.peer.max_bytes):
+                buf = self.peer.input_buffer(shape, x.dtype)
+                torch.matmul(x, weight.t(), out=buf)
+                return self.peer.all_reduce(buf)
+        return self.all_reduce(torch.nn.functional.linear(x, weight))
+
+    def close(self) -> None:
+        if self.peer is not None:
+            self.peer.close()
+            self.peer = None
 
 
 def attention_out_proj(attn_out: torch.Tensor, wo_local: torch.Tensor,

@@ -222,6 +222,27 @@ CWM_API int cwm_block_copy(const uint64_t* dst_ptrs, const uint64_t* src_ptrs, i
                            int64_t rows, int64_t row_bytes, int64_t dst_pitch_bytes,
                            int64_t src_pitch_bytes, void* stream);
 
+/* Sum all-reduce over the GPUs of one node through peer memory, for the row-parallel
+ * products of a tensor-parallel layer (the custom all-reduce that
+ * Collectives.all_reduce prefers below 8 MiB, cwm/fastgen/utils/collectives.py:28-45,
+ * 73-88).  Every rank calls it with the same n_elems, in the same order, on a stream
+ * that is behind the producer of its input.  in_ptrs / red_ptrs / flag_ptrs are HOST
+ * arrays of `world` device addresses, entry p being rank p's buffer as this process
+ * can address it (its own allocation for p == rank, an IPC mapping otherwise):
+ *   in    n_elems elements, rank p's input (left unchanged);
+ *   red   n_elems / world elements of scratch;
+ *   flags cwm_allreduce_flag_ints() int32, zero-filled once when allocated.
+ * out: n_elems elements, local.  epoch: two local int32 {1, 0} set once at allocation
+ * and owned by the library afterwards.  n_elems must be a multiple of 8 * world; bf16
+ * or fp16 with fp32 accumulation in rank order (all ranks get identical results).
+ * Waits on peers are bounded; one that runs out sets status bit 2.  Calls that share
+ * buffers must not overlap (one stream, or otherwise ordered). */
+CWM_API int cwm_allreduce(const uint64_t* in_ptrs, const uint64_t* red_ptrs,
+                          const uint64_t* flag_ptrs, void* out, int32_t* epoch, int64_t n_elems,
+                          int dtype, int rank, int world, void* stream);
+CWM_API int cwm_allreduce_flag_ints(void);
+CWM_API int cwm_allreduce_ctas(int64_t n_elems, int world);
+
 /* Token sampling over x[rows, vocab] (fp32, row stride row_stride elements): one
  * launch does what FastGen._sample does with several torch calls,
  * cwm/fastgen/generate.py:996-1014 with cwm/fastgen/utils/sampling.py:6-45.
