@@ -325,6 +325,9 @@ def main() -> None:
                     help="how many times the timed region of K steps is run (the median is reported)")
     ap.add_argument("--only-decode", action="store_true",
                     help="default workload without the prefill / decode_local / decoder blocks")
+    ap.add_argument("--all-reduce", default="nccl", choices=["nccl", "peer"],
+                    help="decoder workload: the process group's all-reduce, or this package's "
+                         "peer-memory kernel for the row-parallel sums")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--as-shard", type=int, default=1,
@@ -841,7 +844,8 @@ def _gather_cat(t: torch.Tensor, dim: int, world: int, dist) -> torch.Tensor:
     return torch.cat(parts, dim=dim)
 
 
-def decoder_parity(margs, rank: int, world: int, dev, dist, ctx: int, collectives: bool) -> dict:
+def decoder_parity(margs, rank: int, world: int, dev, dist, ctx: int, collectives: bool,
+                   peer: bool = False) -> dict:
     """One decode step of a two-layer model with the real layer shapes (and a small
     vocabulary), tensor-parallel over the same ranks, against the CPU oracle of the
     unsharded model built from the gathered weights and caches: checks sharding,
@@ -853,7 +857,8 @@ def decoder_parity(margs, rank: int, world: int, dev, dist, ctx: int, collective
 
     small = dataclasses.replace(margs, n_layers=2, vocab_size=8192)
     shard_of = world if collectives else 1
-    model = ShardedDecoder(small, rank if collectives else 0, shard_of, dev, seed=7)
+    model = ShardedDecoder(small, rank if collectives else 0, shard_of, dev, seed=7,
+                           peer_all_reduce=peer and collectives and world > 1)
     batch = 2
     cols = (ctx + 2 + PAGE - 1) // PAGE
     n_pages = batch * cols
@@ -911,6 +916,9 @@ def decoder_parity(margs, rank: int, world: int, dev, dist, ctx: int, collective
                              "from the gathered weights and cache rows; logits of rank 0"}
         if not err <= 3e-2 * scale:
             raise SystemExit(f"decoder parity check failed: max-abs {err} vs scale {scale}")
+    if model.coll is not None:
+        torch.cuda.synchronize()
+        model.coll.close()
     del model, cache, before, full_caches, layers, emb, out_w
     torch.cuda.empty_cache()
     return result
@@ -935,7 +943,7 @@ def run_decoder(args, rank: int, local_rank: int, world: int, dist, steps: int,
             raise SystemExit("--as-shard needs a single process")
         shard_of = args.as_shard
     parity = decoder_parity(margs, rank, world, dev, dist, min(ctx, 16384),
-                            collectives=shard_of == world)
+                            collectives=shard_of == world, peer=args.all_reduce == "peer")
     total_steps = max(3, args.warmup) + steps * args.repeats + 4
     cols = (ctx + total_steps + PAGE - 1) // PAGE
     n_pages = batch * cols
@@ -945,7 +953,8 @@ def run_decoder(args, rank: int, local_rank: int, world: int, dist, steps: int,
         raise SystemExit(f"decoder workload needs {kv_gb:.0f} GB of KV cache per GPU, "
                          f"{free_gb:.0f} GB free: use more GPUs or smaller --decoder-* values")
     model = ShardedDecoder(margs, rank if shard_of == world else 0, shard_of, dev, seed=5,
-                           collectives=shard_of == world)
+                           collectives=shard_of == world,
+                           peer_all_reduce=args.all_reduce == "peer" and shard_of == world and world > 1)
     cache = model.build_cache(n_pages * PAGE)
     cache.caches[0].normal_()
     for c in cache.caches[1:]:
@@ -1014,7 +1023,9 @@ def run_decoder(args, rank: int, local_rank: int, world: int, dist, steps: int,
                    **({"as_shard": f"one GPU running rank 0 of {shard_of}, no collectives"}
                       if shard_of != world else {}),
                    "launch": "one CUDA-graph replay per step", "logits_finite": finite,
-                   "sampling": "excluded"},
+                   "sampling": "excluded",
+                   "all_reduce": "peer-memory kernel (cwm_allreduce)" if args.all_reduce == "peer"
+                                 and world > 1 else "process group (NCCL)"},
         "parity": parity, "setup_s": round(setup_s, 1),
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "lower_bound_ms": bound_ms, "frac": bound_ms / ms_per_step,
@@ -1025,7 +1036,11 @@ def run_decoder(args, rank: int, local_rank: int, world: int, dist, steps: int,
     }
     if rank == 0 and world == 1 and with_cpu:  # single-process runs only
         line["cpu_baseline"] = cpu_decoder_baseline(margs, batch, ctx, args.cpu_seconds)
-    del graph, logits, model, cache
+    del graph, logits
+    if model.coll is not None:
+        sync_all()
+        model.coll.close()  # collective: unmap peers, barrier, free
+    del model, cache
     torch.cuda.empty_cache()
     return line
 

@@ -60,6 +60,10 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p],
     ),
     "cwm_allreduce_flag_ints": (c_int, []),
+    "cwm_peer_alloc": (c_int, [c_size_t, ctypes.POINTER(c_void_p), c_void_p]),
+    "cwm_peer_open": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "cwm_peer_close": (c_int, [c_void_p]),
+    "cwm_peer_free": (c_int, [c_void_p]),
     "cwm_allreduce_ctas": (c_int, [c_int64, c_int]),
     "cwm_silu_mul": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "cwm_paged_attn_workspace_bytes": (c_size_t, [c_int, c_int64, c_int, c_int, c_int]),

@@ -219,3 +219,52 @@ extern "C" int cwm_allreduce(const uint64_t* in_ptrs, const uint64_t* red_ptrs,
   CWM_CUDA_CHECK(cudaGetLastError());
   return CWM_OK;
 }
+
+// ---- buffers that other processes of the node can map (CUDA IPC) ---------------------
+// Allocated with cudaMalloc outside any framework allocator, so that the IPC handle
+// names exactly this allocation, and opened with the *caller's* device current, which
+// is what makes the runtime enable peer access from the caller's GPU to the owner's.
+extern "C" int cwm_peer_alloc(size_t bytes, void** ptr, void* handle64) {
+  if (!ptr || !handle64 || bytes == 0) {
+    set_error("peer_alloc: bad argument");
+    return CWM_ERR_INVALID;
+  }
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  void* p = nullptr;
+  CWM_CUDA_CHECK(cudaMalloc(&p, bytes));
+  cudaError_t err = cudaMemset(p, 0, bytes);
+  cudaIpcMemHandle_t h;
+  if (err == cudaSuccess) err = cudaIpcGetMemHandle(&h, p);
+  if (err == cudaSuccess) err = cudaDeviceSynchronize();
+  if (err != cudaSuccess) {
+    cudaFree(p);
+    set_error("peer_alloc: %s", cudaGetErrorString(err));
+    return CWM_ERR_CUDA;
+  }
+  memcpy(handle64, &h, sizeof(h));
+  *ptr = p;
+  return CWM_OK;
+}
+
+extern "C" int cwm_peer_open(const void* handle64, void** ptr) {
+  if (!ptr || !handle64) {
+    set_error("peer_open: bad argument");
+    return CWM_ERR_INVALID;
+  }
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  void* p = nullptr;
+  CWM_CUDA_CHECK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *ptr = p;
+  return CWM_OK;
+}
+
+extern "C" int cwm_peer_close(void* ptr) {
+  if (ptr) CWM_CUDA_CHECK(cudaIpcCloseMemHandle(ptr));
+  return CWM_OK;
+}
+
+extern "C" int cwm_peer_free(void* ptr) {
+  if (ptr) CWM_CUDA_CHECK(cudaFree(ptr));
+  return CWM_OK;
+}

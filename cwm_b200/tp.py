@@ -65,23 +65,35 @@ def shard_cache_rows(full_rows: torch.Tensor, shard: HeadShard, n_kv_heads: int,
     return torch.cat([k[:, sl], v[:, sl]], dim=1).contiguous()
 
 
+class _RawCuda:
+    """Raw device memory as an object ``torch.as_tensor`` can wrap (uint8)."""
+
+    def __init__(self, ptr: int, nbytes: int) -> None:
+        self.__cuda_array_interface__ = {
+            "shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+        }
+
+
 class PeerAllReduce:
     """The node-local all-reduce kernel of this package (``cwm_allreduce``) with its
     buffers: the counterpart of the reference's ``CustomAllreduce``
     (``cwm/fastgen/utils/collectives.py:11-15,39-45``).
 
     Each rank allocates an input buffer, a scratch buffer for its reduced slice and
-    a flag array, and maps the other ranks' three buffers through CUDA IPC (the
-    ranks are processes on one node).  ``input_buffer`` hands out a view of the
-    input buffer for the producer (a GEMM with ``out=``) to write into, so that no
-    copy is needed; ``all_reduce`` takes such a view, or copies any other tensor in.
-    Results are new tensors.  ``close`` drops the mappings; call it on every rank,
-    with a barrier before any rank exits, so that no rank unmaps memory a peer's
-    kernel could still read.
+    a flag array through ``cwm_peer_alloc`` and maps the other ranks' three buffers
+    through CUDA IPC (the ranks are processes on one node; the 64-byte handles travel
+    through the process group).  ``input_buffer`` hands out a view of the input
+    buffer for the producer (a GEMM with ``out=``) to write into, so that no copy is
+    needed; ``all_reduce`` takes such a view, or copies any other tensor in.  Results
+    are new tensors.  ``close`` is a collective call: every rank unmaps its peers,
+    all meet at a barrier, then each frees its own buffers, so that no rank releases
+    memory that a peer still maps.
     """
 
     def __init__(self, group: dist.ProcessGroup | None, device: torch.device,
                  max_bytes: int = 8 << 20) -> None:
+        import ctypes
+
         from . import _lib
 
         self.group = group
@@ -91,28 +103,33 @@ class PeerAllReduce:
             raise ValueError("the peer all-reduce serves at most 8 ranks of one node")
         self.device = device
         self.max_bytes = max_bytes
-        lib = _lib.load()
-        self._in = torch.zeros(max_bytes, dtype=torch.uint8, device=device)
-        self._red = torch.zeros(max_bytes // self.world + 16, dtype=torch.uint8, device=device)
-        self._flags = torch.zeros(lib.cwm_allreduce_flag_ints(), dtype=torch.int32, device=device)
-        self._epoch = torch.tensor([1, 0], dtype=torch.int32, device=device)
-        torch.cuda.synchronize(device)
-        self._mapped: list = []  # keeps the peers' storages mapped
+        self._lib = _lib.load()
+        sizes = [max_bytes, max_bytes // self.world + 16, self._lib.cwm_allreduce_flag_ints() * 4]
+        self._own: list[int] = []
+        self._peers: list[int] = []
         self._tables = []
-        for t in (self._in, self._red, self._flags):
-            handle = t.untyped_storage()._share_cuda_()
-            offset = t.storage_offset() * t.element_size()
-            gathered: list = [None] * self.world
-            dist.all_gather_object(gathered, (handle, offset), group=group)
-            ptrs = []
-            for p, (h, off) in enumerate(gathered):
-                if p == self.rank:
-                    ptrs.append(t.data_ptr())
-                    continue
-                storage = torch.UntypedStorage._new_shared_cuda(*h)
-                self._mapped.append(storage)
-                ptrs.append(storage.data_ptr() + off)
-            self._tables.append((ctypes_array(ptrs), ptrs))
+        with torch.cuda.device(device):
+            for nbytes in sizes:
+                ptr = ctypes.c_void_p()
+                handle = ctypes.create_string_buffer(64)
+                _lib.check(self._lib.cwm_peer_alloc(nbytes, ctypes.byref(ptr), handle), "peer_alloc")
+                self._own.append(ptr.value)
+                gathered: list = [None] * self.world
+                dist.all_gather_object(gathered, bytes(handle.raw), group=group)
+                ptrs = []
+                for p, h in enumerate(gathered):
+                    if p == self.rank:
+                        ptrs.append(ptr.value)
+                        continue
+                    mapped = ctypes.c_void_p()
+                    _lib.check(self._lib.cwm_peer_open(ctypes.create_string_buffer(h, 64),
+                                                       ctypes.byref(mapped)), "peer_open")
+                    self._peers.append(mapped.value)
+                    ptrs.append(mapped.value)
+                self._tables.append(ctypes_array(ptrs))
+            self._in = torch.as_tensor(_RawCuda(self._own[0], max_bytes), device=device)
+            self._epoch = torch.tensor([1, 0], dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
     def input_buffer(self, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
@@ -135,11 +152,11 @@ class PeerAllReduce:
         n = x.numel()
         if n * x.element_size() > self.max_bytes:
             raise ValueError("tensor exceeds the all-reduce buffer")
-        if x.data_ptr() != self._in.data_ptr():
+        if x.data_ptr() != self._own[0]:
             self.input_buffer(tuple(x.shape), x.dtype).copy_(x)
         out = torch.empty_like(x)
         code = _lib.load().cwm_allreduce(
-            self._tables[0][0], self._tables[1][0], self._tables[2][0], out.data_ptr(),
+            self._tables[0], self._tables[1], self._tables[2], out.data_ptr(),
             self._epoch.data_ptr(), n, _DTYPES[x.dtype], self.rank, self.world, _stream(x))
         _lib.check(code, "allreduce")
         return out
@@ -150,8 +167,20 @@ class PeerAllReduce:
                 and x.numel() * x.element_size() <= self.max_bytes)
 
     def close(self) -> None:
-        self._mapped.clear()
-        self._tables.clear()
+        """Collective: unmap the peers' buffers, barrier, free the own buffers."""
+        if not self._own:
+            return
+        torch.cuda.synchronize(self.device)
+        with torch.cuda.device(self.device):
+            for ptr in self._peers:
+                self._lib.cwm_peer_close(ptr)
+            self._peers = []
+            dist.barrier(group=self.group)
+            self._in = None
+            for ptr in self._own:
+                self._lib.cwm_peer_free(ptr)
+            self._own = []
+        self._tables = []
 
 
 def ctypes_array(values: list[int]):

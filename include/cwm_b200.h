@@ -5,7 +5,8 @@
  * of this path is the set of Python call signatures used by
  * cwm/fastgen/forward.py.  Each entry point below replaces one of them and cites
  * it.  All pointers are device pointers unless stated otherwise, all tensors are
- * owned by the caller, nothing here allocates device memory, and every launch
+ * owned by the caller, nothing here allocates device memory (except cwm_peer_alloc,
+ * a set-up call), and every launch
  * goes to the stream given (a cudaStream_t passed as void*).  Calls are
  * asynchronous and may be captured in a CUDA graph unless stated otherwise.
  *
@@ -242,6 +243,20 @@ CWM_API int cwm_allreduce(const uint64_t* in_ptrs, const uint64_t* red_ptrs,
                           int dtype, int rank, int world, void* stream);
 CWM_API int cwm_allreduce_flag_ints(void);
 CWM_API int cwm_allreduce_ctas(int64_t n_elems, int world);
+
+/* Set-up of the buffers that cwm_allreduce shares between the processes of a node
+ * (the only entry points of this library that allocate device memory; call them once
+ * at start-up).  cwm_peer_alloc: cudaMalloc of `bytes` zero-filled bytes on the current
+ * device plus its 64-byte CUDA IPC handle, to be sent to the other processes by any
+ * host channel.  cwm_peer_open: maps a peer's buffer into this process with the
+ * caller's device current (this is what enables peer access from the caller's GPU to
+ * the owner's); the owner must outlive the mapping.  cwm_peer_close unmaps,
+ * cwm_peer_free releases an own buffer: close every mapping on every process, meet at
+ * a barrier, then free. */
+CWM_API int cwm_peer_alloc(size_t bytes, void** ptr, void* handle64);
+CWM_API int cwm_peer_open(const void* handle64, void** ptr);
+CWM_API int cwm_peer_close(void* ptr);
+CWM_API int cwm_peer_free(void* ptr);
 
 /* Token sampling over x[rows, vocab] (fp32, row stride row_stride elements): one
  * launch does what FastGen._sample does with several torch calls,
