@@ -438,13 +438,19 @@ def main() -> None:
                         "steps per chunk call after 3 warm-up steps",
             }
         if n_gpus == 8:
-            dec = run_decoder(args, rank, local_rank, world, dist, steps=20, with_cpu=False)
-            line["decoder"] = {
-                "tokens_per_s": dec["value"], "ms_per_step": dec["ms_per_step"],
-                "frac_of_hbm_bound": dec["roofline"]["frac"], "parity": dec["parity"],
-                "setup_s": dec["setup_s"], "config": dec["config"],
-                "all_reduce": dec.get("all_reduce"),
-            }
+            def summary(dec):
+                return {"tokens_per_s": dec["value"], "ms_per_step": dec["ms_per_step"],
+                        "ms_per_step_runs": dec["ms_per_step_runs"],
+                        "frac_of_hbm_bound": dec["roofline"]["frac"], "parity": dec["parity"],
+                        "setup_s": dec["setup_s"], "config": dec["config"],
+                        "all_reduce": dec.get("all_reduce")}
+
+            args.all_reduce = "peer"
+            line["decoder"] = summary(run_decoder(args, rank, local_rank, world, dist, steps=20,
+                                                  with_cpu=False))
+            args.all_reduce = "nccl"
+            line["decoder_nccl"] = summary(run_decoder(args, rank, local_rank, world, dist,
+                                                       steps=20, with_cpu=False))
         line["extra_blocks_s"] = round(time.time() - t_extra, 1)
     if rank == 0:
         print(json.dumps(line))
@@ -989,6 +995,33 @@ def run_decoder(args, rank: int, local_rank: int, world: int, dist, steps: int,
     for _ in range(max(3, args.warmup)):
         step()
     sync_all()
+    # latency of one all-reduce of the step's message, 32 in a row inside a graph
+    ar_us = None
+    if model.coll is not None:
+        coll = model.coll
+        msg = (coll.peer.input_buffer((batch, margs.dim), torch.bfloat16) if coll.peer is not None
+               else torch.zeros(batch, margs.dim, dtype=torch.bfloat16, device=dev))
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            coll.all_reduce(msg)
+        torch.cuda.current_stream().wait_stream(side)
+        sync_all()
+        ar_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(ar_graph):
+            for _ in range(32):
+                coll.all_reduce(msg)
+        ar_graph.replay()
+        sync_all()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(5):
+            ar_graph.replay()
+        a1.record()
+        sync_all()
+        t_ar = torch.tensor([a0.elapsed_time(a1)], device=dev)
+        dist.all_reduce(t_ar, op=dist.ReduceOp.MAX)
+        ar_us = float(t_ar.item()) * 1e3 / (5 * 32)
+        del ar_graph
     setup_s = time.time() - t_setup
     runs = []
     with ClockSampler(local_rank) as clocks:
@@ -1027,6 +1060,9 @@ def run_decoder(args, rank: int, local_rank: int, world: int, dist, steps: int,
                    "all_reduce": "peer-memory kernel (cwm_allreduce)" if args.all_reduce == "peer"
                                  and world > 1 else "process group (NCCL)"},
         "parity": parity, "setup_s": round(setup_s, 1),
+        "all_reduce": {"us_per_call": ar_us, "bytes": batch * margs.dim * 2,
+                       "calls_per_step": 2 * margs.n_layers + 1,
+                       "note": "32 back-to-back calls replayed from a graph, max over ranks"},
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "lower_bound_ms": bound_ms, "frac": bound_ms / ms_per_step,
                      "kv_bytes_per_gpu": kv_bytes, "weight_bytes_per_gpu": w_bytes,
