@@ -30,7 +30,7 @@ namespace cwm {
 namespace {
 
 constexpr int kArThreads = 256;
-constexpr int kArMaxCtas = 64;
+constexpr int kArMaxCtas = 128;
 constexpr int kArMaxWorld = 8;
 constexpr long long kArSpinLimit = 1ll << 24;  // polls of a flag before giving up
 
@@ -126,13 +126,17 @@ __global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArArgs a) {
   }
   // ---- all-gather: every rank's reduced slice into the local output
   if (ok) {
-    for (int p = 0; p < a.world; ++p) {
-      const int src = (a.rank + p) % a.world;  // start with the local slice, spread the peers
-      const uint4* from = a.red[src];
-      uint4* to = a.out + static_cast<long long>(src) * a.slice_vecs;
-      for (long long i = static_cast<long long>(blockIdx.x) * kArThreads + threadIdx.x;
-           i < a.slice_vecs; i += static_cast<long long>(gridDim.x) * kArThreads) {
-        to[i] = from[i];
+    for (long long i = static_cast<long long>(blockIdx.x) * kArThreads + threadIdx.x;
+         i < a.slice_vecs; i += static_cast<long long>(gridDim.x) * kArThreads) {
+      // all peers' loads in flight before the first store
+      uint4 v[kArMaxWorld];
+#pragma unroll
+      for (int p = 0; p < kArMaxWorld; ++p) {
+        if (p < a.world) v[p] = a.red[p][i];
+      }
+#pragma unroll
+      for (int p = 0; p < kArMaxWorld; ++p) {
+        if (p < a.world) a.out[static_cast<long long>(p) * a.slice_vecs + i] = v[p];
       }
     }
   } else if (threadIdx.x == 0) {
