@@ -42,10 +42,10 @@ HQ, HKV, D, PAGE = 48, 8, 128, 256
 WINDOW_LOCAL = 8191
 L2_BYTES = 126 * 1024 * 1024
 # DRAM bytes moved per algorithmic byte by the decode kernel, from the ncu capture
-# summarised in profiles/decode_kernel_small_ncu_full.txt (536.97 MB read + written
+# summarised in profiles/decode_kernel_small_ncu_full.txt (538.33 MB read + written
 # for 527.77 MB algorithmic).  The over-fetch is tile granularity at the ends of a
 # context, so it grows in proportion to the work.
-DECODE_TRAFFIC_RATIO = 536.97 / 527.77
+DECODE_TRAFFIC_RATIO = 538.33 / 527.77
 
 
 # ------------------------------------------------------------------ workloads
