@@ -999,8 +999,7 @@ def run_decoder(args, rank: int, local_rank: int, world: int, dist, steps: int,
     ar_us = None
     if model.coll is not None:
         coll = model.coll
-        msg = (coll.peer.input_buffer((batch, margs.dim), torch.bfloat16) if coll.peer is not None
-               else torch.zeros(batch, margs.dim, dtype=torch.bfloat16, device=dev))
+        msg = torch.zeros(batch, margs.dim, dtype=torch.bfloat16, device=dev)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             coll.all_reduce(msg)

@@ -1,27 +1,27 @@
 // Sum all-reduce of a small activation tensor over the GPUs of one node, as one
-// kernel over peer memory (NVLink / NVSwitch loads and stores), for the
-// row-parallel products of a tensor-parallel decoder layer.
+// kernel over peer memory (NVLink / NVSwitch stores), for the row-parallel products
+// of a tensor-parallel decoder layer.
 //
 // The reference engine sends these messages (batch x 6144 bf16 = 1.5 MB in decode)
-// through a custom one-shot all-reduce below 8 MiB and through NCCL otherwise
-// (cwm/fastgen/utils/collectives.py:28-45,73-88).  At this size the cost is
-// latency: a two-shot exchange moves 2 * (world - 1) / world of the message per GPU
-// and needs two rounds of flags.
-//
-// Every rank owns three buffers that all ranks can address: `in` (the GEMM writes
-// its output there), `red` (this rank's reduced slice) and a small array of flags.
-// One launch on every rank:
-//   1. flag round 0: "my input is complete" (the launch is behind the GEMM in the
-//      stream) to every peer, wait for the same from every peer;
-//   2. reduce-scatter: rank r sums slice r of all ranks' `in` in rank order with
-//      fp32 accumulation (every rank later copies the same rounded values, so all
-//      ranks end with identical results) into its `red`;
-//   3. flag round 1: "my slice is reduced";
-//   4. all-gather: copy every rank's `red` slice into the local output.
-// Flags carry an epoch that each launch advances, so nothing is ever reset and the
-// launch can be replayed from a CUDA graph.  Each CTA synchronises with the CTA of
-// the same index on the other ranks only, through its own flag slots.  Every wait
-// is bounded; a wait that runs out sets status bit 2 and the kernel returns.
+// through a custom all-reduce below 8 MiB and through NCCL otherwise
+// (cwm/fastgen/utils/collectives.py:28-45,73-88).  At this size the cost is latency,
+// so the exchange is built from posted remote *stores* (one way across the switch)
+// rather than remote loads (a round trip each):
+//   1. every rank pushes slice p of its input into rank p's scratch (slot = sender),
+//      then raises a flag at rank p;
+//   2. rank p, once the flags of all senders are up, sums the slots of its scratch
+//      in rank order with fp32 accumulation (local reads) and pushes the rounded
+//      slice into every rank's result buffer, then raises a second flag everywhere;
+//   3. a rank returns when the second flags of all ranks are up: its result buffer
+//      is complete, and bit-identical to every other rank's.
+// No "input ready" round is needed (a rank pushes its own data), and the flags carry
+// an epoch that each launch advances, so nothing is ever reset and the launch can be
+// replayed from a CUDA graph.  Each CTA synchronises with the CTA of the same index
+// on the other ranks only, through its own flag slots.  Every wait is bounded; one
+// that runs out sets status bit 2 and the kernel returns.  Buffer reuse is safe
+// without further rounds: a rank starts its next call only after it has received
+// every rank's reduced slice, i.e. after every rank has finished reading the
+// scratch this rank will push into next.
 #include <string.h>
 
 #include "common.cuh"
@@ -35,11 +35,11 @@ constexpr int kArMaxWorld = 8;
 constexpr long long kArSpinLimit = 1ll << 24;  // polls of a flag before giving up
 
 struct ArArgs {
-  const uint4* in[kArMaxWorld];   // every rank's input buffer
-  const uint4* red[kArMaxWorld];  // every rank's reduced-slice buffer
-  int* flags[kArMaxWorld];        // every rank's flags: [2 rounds][kArMaxCtas][kArMaxWorld]
-  uint4* out;                     // local result
-  int* epoch;                     // local: [0] epoch of this launch, [1] CTAs finished
+  const uint4* in;                  // local input
+  uint4* scratch[kArMaxWorld];      // every rank's scratch: [world slots][slice]
+  uint4* result[kArMaxWorld];       // every rank's result buffer
+  int* flags[kArMaxWorld];          // every rank's flags: [2 rounds][kArMaxCtas][kArMaxWorld]
+  int* epoch;                       // local: [0] epoch of this launch, [1] CTAs finished
   int* status;
   long long slice_vecs;  // 16-byte vectors per rank's slice
   int rank;
@@ -55,12 +55,13 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   return v;
 }
 
-// All ranks' CTAs of this index meet: thread t < world tells rank t and then waits
-// for rank t's word.  Returns false (for the whole CTA) when a wait ran out.
+// Thread t < world tells rank t "my part of this round is written", then waits for
+// rank t's word.  Returns false (for the whole CTA) when a wait ran out.
 __device__ __forceinline__ bool flag_round(const ArArgs& a, int round, int epoch) {
   __shared__ int failed;
   if (threadIdx.x == 0) failed = 0;
-  __syncthreads();  // also: every thread's earlier writes precede the release below
+  __threadfence_system();  // this thread's pushes are ordered before the flags below
+  __syncthreads();         // ... and so are every other thread's of the CTA
   if (threadIdx.x < a.world) {
     const int peer = threadIdx.x;
     const int slot = (round * kArMaxCtas + blockIdx.x) * kArMaxWorld;
@@ -97,17 +98,29 @@ __device__ __forceinline__ void accumulate(float (&acc)[8], uint4 v) {
 template <bool kBf16>
 __global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArArgs a) {
   const int epoch = *a.epoch;
+  const long long first = static_cast<long long>(blockIdx.x) * kArThreads + threadIdx.x;
+  const long long step = static_cast<long long>(gridDim.x) * kArThreads;
+  // ---- 1. push slice p of my input into rank p's scratch, slot = my rank
+  for (long long i = first; i < a.slice_vecs; i += step) {
+    uint4 v[kArMaxWorld];
+#pragma unroll
+    for (int p = 0; p < kArMaxWorld; ++p) {
+      if (p < a.world) v[p] = a.in[static_cast<long long>(p) * a.slice_vecs + i];
+    }
+#pragma unroll
+    for (int p = 0; p < kArMaxWorld; ++p) {
+      if (p < a.world) a.scratch[p][static_cast<long long>(a.rank) * a.slice_vecs + i] = v[p];
+    }
+  }
   bool ok = flag_round(a, 0, epoch);
-  // ---- reduce-scatter: my slice of everybody's input, summed in rank order
+  // ---- 2. sum my slice over the senders in rank order, push the result everywhere
   if (ok) {
-    const long long base = static_cast<long long>(a.rank) * a.slice_vecs;
-    uint4* my_red = const_cast<uint4*>(a.red[a.rank]);
-    for (long long i = static_cast<long long>(blockIdx.x) * kArThreads + threadIdx.x;
-         i < a.slice_vecs; i += static_cast<long long>(gridDim.x) * kArThreads) {
+    const uint4* mine = a.scratch[a.rank];
+    for (long long i = first; i < a.slice_vecs; i += step) {
       uint4 v[kArMaxWorld];
 #pragma unroll
       for (int p = 0; p < kArMaxWorld; ++p) {
-        if (p < a.world) v[p] = a.in[p][base + i];
+        if (p < a.world) v[p] = mine[static_cast<long long>(p) * a.slice_vecs + i];
       }
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -119,29 +132,15 @@ __global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArArgs a) {
       r.y = pack2<kBf16>(acc[2], acc[3]);
       r.z = pack2<kBf16>(acc[4], acc[5]);
       r.w = pack2<kBf16>(acc[6], acc[7]);
-      my_red[i] = r;
+#pragma unroll
+      for (int p = 0; p < kArMaxWorld; ++p) {
+        if (p < a.world) a.result[p][static_cast<long long>(a.rank) * a.slice_vecs + i] = r;
+      }
     }
-    __threadfence_system();
+    // ---- 3. my result buffer is complete when every rank's slice has landed
     ok = flag_round(a, 1, epoch);
   }
-  // ---- all-gather: every rank's reduced slice into the local output
-  if (ok) {
-    for (long long i = static_cast<long long>(blockIdx.x) * kArThreads + threadIdx.x;
-         i < a.slice_vecs; i += static_cast<long long>(gridDim.x) * kArThreads) {
-      // all peers' loads in flight before the first store
-      uint4 v[kArMaxWorld];
-#pragma unroll
-      for (int p = 0; p < kArMaxWorld; ++p) {
-        if (p < a.world) v[p] = a.red[p][i];
-      }
-#pragma unroll
-      for (int p = 0; p < kArMaxWorld; ++p) {
-        if (p < a.world) a.out[static_cast<long long>(p) * a.slice_vecs + i] = v[p];
-      }
-    }
-  } else if (threadIdx.x == 0) {
-    atomicOr(a.status, DEV_WAIT_TIMEOUT);
-  }
+  if (!ok && threadIdx.x == 0) atomicOr(a.status, DEV_WAIT_TIMEOUT);
   // ---- the last CTA to finish advances the epoch for the next launch
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -170,11 +169,12 @@ extern "C" int cwm_allreduce_ctas(int64_t n_elems, int world) {
 
 extern "C" int cwm_allreduce_flag_ints(void) { return 2 * kArMaxCtas * kArMaxWorld; }
 
-extern "C" int cwm_allreduce(const uint64_t* in_ptrs, const uint64_t* red_ptrs,
-                             const uint64_t* flag_ptrs, void* out, int32_t* epoch,
-                             int64_t n_elems, int dtype, int rank, int world, void* stream) {
+extern "C" int cwm_allreduce(const void* in, const uint64_t* scratch_ptrs,
+                             const uint64_t* result_ptrs, const uint64_t* flag_ptrs,
+                             int32_t* epoch, int64_t n_elems, int dtype, int rank, int world,
+                             void* stream) {
   if (n_elems == 0) return CWM_OK;
-  if (!in_ptrs || !red_ptrs || !flag_ptrs || !out || !epoch) {
+  if (!in || !scratch_ptrs || !result_ptrs || !flag_ptrs || !epoch) {
     set_error("allreduce: null pointer");
     return CWM_ERR_INVALID;
   }
@@ -186,24 +186,24 @@ extern "C" int cwm_allreduce(const uint64_t* in_ptrs, const uint64_t* red_ptrs,
     set_error("allreduce: bf16 and fp16 only");
     return CWM_ERR_UNSUPPORTED;
   }
-  if (n_elems % (8ll * world) != 0) {
-    set_error("allreduce: %lld elements do not split into 16-byte vectors over %d ranks",
-              static_cast<long long>(n_elems), world);
+  if (n_elems % (8ll * world) != 0 || reinterpret_cast<uintptr_t>(in) % 16 != 0) {
+    set_error("allreduce: %lld elements must split into 16-byte vectors over %d ranks, and the "
+              "input must be 16-byte aligned", static_cast<long long>(n_elems), world);
     return CWM_ERR_UNSUPPORTED;
   }
   ArArgs a;
   memset(&a, 0, sizeof(a));
   for (int p = 0; p < world; ++p) {
-    if (in_ptrs[p] % 16 || red_ptrs[p] % 16 || flag_ptrs[p] % 4 || !in_ptrs[p] || !red_ptrs[p] ||
-        !flag_ptrs[p]) {
+    if (scratch_ptrs[p] % 16 || result_ptrs[p] % 16 || flag_ptrs[p] % 4 || !scratch_ptrs[p] ||
+        !result_ptrs[p] || !flag_ptrs[p]) {
       set_error("allreduce: peer buffer %d is null or misaligned", p);
       return CWM_ERR_INVALID;
     }
-    a.in[p] = reinterpret_cast<const uint4*>(in_ptrs[p]);
-    a.red[p] = reinterpret_cast<const uint4*>(red_ptrs[p]);
+    a.scratch[p] = reinterpret_cast<uint4*>(scratch_ptrs[p]);
+    a.result[p] = reinterpret_cast<uint4*>(result_ptrs[p]);
     a.flags[p] = reinterpret_cast<int*>(flag_ptrs[p]);
   }
-  a.out = static_cast<uint4*>(out);
+  a.in = static_cast<const uint4*>(in);
   a.epoch = epoch;
   a.status = status_word();
   if (a.status == nullptr) {

@@ -69,16 +69,32 @@ __device__ __forceinline__ void for_each(const Row& r, F&& f) {
   // f(index, raw value); chunk c covers indices [c * kChunk, (c + 1) * kChunk)
   const int tid = threadIdx.x;
   if (r.vec4) {
+    // four 16-byte loads in flight per thread before the first use: a row is streamed
+    // by one CTA, so the loop is bound by memory latency unless loads are batched
     const float4* x4 = reinterpret_cast<const float4*>(r.x);
     const long long n4 = r.n >> 2;
-    for (long long i = tid; i < n4; i += kThreads) {
+    long long i = tid;
+    for (; i + 3 * kThreads < n4; i += 4 * kThreads) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = x4[i + u * kThreads];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long b = 4 * (i + u * kThreads);
+        f(b, v[u].x);
+        f(b + 1, v[u].y);
+        f(b + 2, v[u].z);
+        f(b + 3, v[u].w);
+      }
+    }
+    for (; i < n4; i += kThreads) {
       const float4 v = x4[i];
       f(4 * i, v.x);
       f(4 * i + 1, v.y);
       f(4 * i + 2, v.z);
       f(4 * i + 3, v.w);
     }
-    for (long long i = (n4 << 2) + tid; i < r.n; i += kThreads) f(i, r.x[i]);
+    for (long long j = (n4 << 2) + tid; j < r.n; j += kThreads) f(j, r.x[j]);
   } else {
     for (long long base = 0; base < r.n; base += kChunk) {
 #pragma unroll

@@ -165,7 +165,10 @@ class ShardedDecoder:
         idx = torch.where(mask, torch.zeros_like(tokens), tokens - start)
         h = F.embedding(idx, self.tok_embeddings)
         h = h.masked_fill(mask[:, None], 0.0)
-        return self._all_reduce(h)
+        h = self._all_reduce(h)
+        # the peer kernel returns a view of a buffer that later calls reuse; the
+        # residual stream lives for the whole pass, so it gets memory of its own
+        return h.clone() if self.coll is not None and self.coll.peer is not None else h
 
     def _forward(self, tokens: torch.Tensor, bias: AttnBias, q_seqpos: torch.Tensor,
                  q_batch: torch.Tensor | None, actual_batch_size: torch.Tensor | None,

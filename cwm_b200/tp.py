@@ -79,15 +79,14 @@ class PeerAllReduce:
     buffers: the counterpart of the reference's ``CustomAllreduce``
     (``cwm/fastgen/utils/collectives.py:11-15,39-45``).
 
-    Each rank allocates an input buffer, a scratch buffer for its reduced slice and
-    a flag array through ``cwm_peer_alloc`` and maps the other ranks' three buffers
-    through CUDA IPC (the ranks are processes on one node; the 64-byte handles travel
-    through the process group).  ``input_buffer`` hands out a view of the input
-    buffer for the producer (a GEMM with ``out=``) to write into, so that no copy is
-    needed; ``all_reduce`` takes such a view, or copies any other tensor in.  Results
-    are new tensors.  ``close`` is a collective call: every rank unmaps its peers,
-    all meet at a barrier, then each frees its own buffers, so that no rank releases
-    memory that a peer still maps.
+    Each rank allocates a scratch buffer, two result buffers and a flag array through
+    ``cwm_peer_alloc`` and maps the other ranks' buffers through CUDA IPC (the ranks
+    are processes on one node; the 64-byte handles travel through the process group).
+    ``all_reduce(x)`` takes any contiguous bf16 / fp16 device tensor and returns the
+    sum as a view of one of the two result buffers, which alternate from call to
+    call: a result stays valid until the second call after it.  ``close`` is a
+    collective call: every rank unmaps its peers, all meet at a barrier, then each
+    frees its own buffers, so that no rank releases memory that a peer still maps.
     """
 
     def __init__(self, group: dist.ProcessGroup | None, device: torch.device,
@@ -104,7 +103,8 @@ class PeerAllReduce:
         self.device = device
         self.max_bytes = max_bytes
         self._lib = _lib.load()
-        sizes = [max_bytes, max_bytes // self.world + 16, self._lib.cwm_allreduce_flag_ints() * 4]
+        # scratch, result 0, result 1, flags
+        sizes = [max_bytes, max_bytes, max_bytes, self._lib.cwm_allreduce_flag_ints() * 4]
         self._own: list[int] = []
         self._peers: list[int] = []
         self._tables = []
@@ -127,44 +127,34 @@ class PeerAllReduce:
                     self._peers.append(mapped.value)
                     ptrs.append(mapped.value)
                 self._tables.append(ctypes_array(ptrs))
-            self._in = torch.as_tensor(_RawCuda(self._own[0], max_bytes), device=device)
+            self._results = [torch.as_tensor(_RawCuda(self._own[1 + i], max_bytes), device=device)
+                             for i in range(2)]
             self._epoch = torch.tensor([1, 0], dtype=torch.int32, device=device)
+        self._calls = 0
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
-    def input_buffer(self, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
-        """A view of the shared input buffer with the given shape (one at a time: the
-        next ``input_buffer`` call returns the same memory)."""
-        n = 1
-        for d in shape:
-            n *= d
-        nbytes = n * torch.empty((), dtype=dtype).element_size()
-        if nbytes > self.max_bytes:
-            raise ValueError(f"{nbytes} bytes exceed the all-reduce buffer of {self.max_bytes}")
-        return self._in[:nbytes].view(dtype).view(shape)
+    def supports(self, x: torch.Tensor) -> bool:
+        return (x.dtype in (torch.bfloat16, torch.float16) and x.is_contiguous()
+                and x.numel() % (8 * self.world) == 0 and x.data_ptr() % 16 == 0
+                and x.numel() * x.element_size() <= self.max_bytes)
 
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         from . import _lib
         from .kernels import _DTYPES, _stream
 
-        if x.dtype not in (torch.bfloat16, torch.float16) or not x.is_contiguous():
-            raise ValueError("the peer all-reduce takes contiguous bf16 or fp16 tensors")
-        n = x.numel()
-        if n * x.element_size() > self.max_bytes:
-            raise ValueError("tensor exceeds the all-reduce buffer")
-        if x.data_ptr() != self._own[0]:
-            self.input_buffer(tuple(x.shape), x.dtype).copy_(x)
-        out = torch.empty_like(x)
+        if not self.supports(x):
+            raise ValueError("the peer all-reduce takes contiguous, 16-byte aligned bf16 or fp16 "
+                             "tensors whose size splits into 16-byte vectors over the ranks and "
+                             "fits its buffers")
+        which = self._calls & 1
+        self._calls += 1
         code = _lib.load().cwm_allreduce(
-            self._tables[0], self._tables[1], self._tables[2], out.data_ptr(),
-            self._epoch.data_ptr(), n, _DTYPES[x.dtype], self.rank, self.world, _stream(x))
+            x.data_ptr(), self._tables[0], self._tables[1 + which], self._tables[3],
+            self._epoch.data_ptr(), x.numel(), _DTYPES[x.dtype], self.rank, self.world, _stream(x))
         _lib.check(code, "allreduce")
-        return out
-
-    def supports(self, x: torch.Tensor) -> bool:
-        return (x.dtype in (torch.bfloat16, torch.float16) and x.is_contiguous()
-                and x.numel() % (8 * self.world) == 0
-                and x.numel() * x.element_size() <= self.max_bytes)
+        nbytes = x.numel() * x.element_size()
+        return self._results[which][:nbytes].view(x.dtype).view(x.shape)
 
     def close(self) -> None:
         """Collective: unmap the peers' buffers, barrier, free the own buffers."""
@@ -176,7 +166,7 @@ class PeerAllReduce:
                 self._lib.cwm_peer_close(ptr)
             self._peers = []
             dist.barrier(group=self.group)
-            self._in = None
+            self._results = []
             for ptr in self._own:
                 self._lib.cwm_peer_free(ptr)
             self._own = []
@@ -195,7 +185,8 @@ class Collectives:
     peer-memory kernel when ``peer`` is given and the tensor qualifies (the
     reference's rule: its custom all-reduce below 8 MiB, ``collectives.py:73-88``),
     through the process group's all-reduce (NCCL on GPUs, gloo in CPU tests)
-    otherwise."""
+    otherwise.  With the peer kernel the result is a view of a buffer that the
+    second next call overwrites; with the process group it is ``x`` itself."""
 
     def __init__(self, group: dist.ProcessGroup | None = None,
                  peer: PeerAllReduce | None = None) -> None:
@@ -211,18 +202,7 @@ class Collectives:
         return x
 
     def linear_all_reduce(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-        """``all_reduce(F.linear(x, weight))`` with the product written straight into
-        the shared input buffer when the peer kernel is used."""
-        if self.peer is not None:
-            shape = (*x.shape[:-1], weight.shape[0])
-            n = 1
-            for d in shape:
-                n *= d
-            if (x.dtype in (torch.bfloat16, torch.float16) and n % (8 * self.tp_size) == 0
-                    and n * x.element_size() <= self.peer.max_bytes):
-                buf = self.peer.input_buffer(shape, x.dtype)
-                torch.matmul(x, weight.t(), out=buf)
-                return self.peer.all_reduce(buf)
+        """``all_reduce(F.linear(x, weight))`` (``forward.py:763-768,782-785``)."""
         return self.all_reduce(torch.nn.functional.linear(x, weight))
 
     def close(self) -> None:

@@ -227,20 +227,23 @@ CWM_API int cwm_block_copy(const uint64_t* dst_ptrs, const uint64_t* src_ptrs, i
  * products of a tensor-parallel layer (the custom all-reduce that
  * Collectives.all_reduce prefers below 8 MiB, cwm/fastgen/utils/collectives.py:28-45,
  * 73-88).  Every rank calls it with the same n_elems, in the same order, on a stream
- * that is behind the producer of its input.  in_ptrs / red_ptrs / flag_ptrs are HOST
- * arrays of `world` device addresses, entry p being rank p's buffer as this process
- * can address it (its own allocation for p == rank, an IPC mapping otherwise):
- *   in    n_elems elements, rank p's input (left unchanged);
- *   red   n_elems / world elements of scratch;
- *   flags cwm_allreduce_flag_ints() int32, zero-filled once when allocated.
- * out: n_elems elements, local.  epoch: two local int32 {1, 0} set once at allocation
- * and owned by the library afterwards.  n_elems must be a multiple of 8 * world; bf16
- * or fp16 with fp32 accumulation in rank order (all ranks get identical results).
- * Waits on peers are bounded; one that runs out sets status bit 2.  Calls that share
- * buffers must not overlap (one stream, or otherwise ordered). */
-CWM_API int cwm_allreduce(const uint64_t* in_ptrs, const uint64_t* red_ptrs,
-                          const uint64_t* flag_ptrs, void* out, int32_t* epoch, int64_t n_elems,
-                          int dtype, int rank, int world, void* stream);
+ * that is behind the producer of its input.  in: n_elems local elements (left
+ * unchanged).  scratch_ptrs / result_ptrs / flag_ptrs are HOST arrays of `world`
+ * device addresses, entry p being rank p's buffer as this process can address it (its
+ * own allocation for p == rank, an IPC mapping otherwise):
+ *   scratch  n_elems elements;
+ *   result   n_elems elements: when the call has run, result_ptrs[rank] holds the sum
+ *            (the same bits on every rank); it is overwritten by the next call that
+ *            is given the same buffers;
+ *   flags    cwm_allreduce_flag_ints() int32, zero-filled once when allocated.
+ * epoch: two local int32 {1, 0} set once at allocation and owned by the library
+ * afterwards.  n_elems must be a multiple of 8 * world; bf16 or fp16 with fp32
+ * accumulation in rank order.  Waits on peers are bounded; one that runs out sets
+ * status bit 2.  Calls that share scratch and flags must not overlap (one stream, or
+ * otherwise ordered). */
+CWM_API int cwm_allreduce(const void* in, const uint64_t* scratch_ptrs,
+                          const uint64_t* result_ptrs, const uint64_t* flag_ptrs, int32_t* epoch,
+                          int64_t n_elems, int dtype, int rank, int world, void* stream);
 CWM_API int cwm_allreduce_flag_ints(void);
 CWM_API int cwm_allreduce_ctas(int64_t n_elems, int world);
 

@@ -313,3 +313,51 @@ def test_randomized_problems(ops):
         window = [-1, 0, 37, 128, 700, 8191][rnd(0, 5)]
         p = make_problem(q_lens, kv, hq=hkv * group, hkv=hkv, page_size=page, seed=1000 + case)
         _check(ops, p, window)
+
+
+def test_decode_never_uses_rows_beyond_the_context(ops):
+    """Rows of the last page at or beyond ``seqused_k`` hold whatever the page held
+    before; filled with NaN and Inf they must not change a bit of the decode output
+    (P = 0 times NaN would otherwise poison the row through the P.V product)."""
+    ctx = [70, 300, 1000, 513, 255, 64, 1]
+    p = make_problem([1] * len(ctx), ctx, hq=12, hkv=2, seed=91)
+    clean, _ = _run(ops, p, -1)
+    clean_w, _ = _run(ops, p, 127)
+    poisoned = make_problem([1] * len(ctx), ctx, hq=12, hkv=2, seed=91)
+    rows = poisoned.cache.view(-1, p.page_size, poisoned.cache.shape[1])
+    for b, n in enumerate(ctx):
+        last = (n - 1) // p.page_size
+        page = int(p.block_table[b, last])
+        rows[page, n - last * p.page_size :] = float("nan")
+        rows[page, n - last * p.page_size :: 2] = float("inf")
+    got, _ = _run(ops, poisoned, -1)
+    got_w, _ = _run(ops, poisoned, 127)
+    assert torch.isfinite(got).all() and torch.isfinite(got_w).all()
+    assert torch.equal(got.view(torch.int16), clean.view(torch.int16))
+    assert torch.equal(got_w.view(torch.int16), clean_w.view(torch.int16))
+    assert _status() == 0
+
+
+def test_too_small_max_seqlen_q_is_reported(ops):
+    """The prefill grid is sized from max_seqlen_q; a caller that understates it gets
+    status bit 4 (part of the output was not computed) instead of silence."""
+    p = make_problem([300, 40], [300, 500], hq=12, hkv=2, seed=92)
+    pg = p.to(DEV)
+    k4, v4 = pg.kv_views()
+    ops.mha_fwd(pg.q, k4, v4, pg.cu_seqlens_q, None, pg.seqused_k, None, 128,
+                p.block_table.shape[1] * p.page_size, 0, pg.block_table, p.d**-0.5, True, -1, -1)
+    torch.cuda.synchronize()
+    assert _status() & 4
+    # one-query sequences although the bounds promised none: the decode kernel did not run
+    p2 = make_problem([1, 3], [50, 60], hq=12, hkv=2, seed=93)
+    pg2 = p2.to(DEV)
+    k4, v4 = pg2.kv_views()
+    cu = torch.tensor([0, 1, 4], dtype=torch.int32, device=DEV)
+    q = torch.randn(4, 12, 128, device=DEV).to(torch.bfloat16)
+    # total_q == batch * max_seqlen_q tells the library that every sequence has 2 queries
+    ops.mha_fwd(q, k4, v4, cu, None, pg2.seqused_k, None, 2, p2.block_table.shape[1] * p2.page_size,
+                0, pg2.block_table, p2.d**-0.5, True, -1, -1)
+    torch.cuda.synchronize()
+    assert _status() & 4
+    good, _ = _run(ops, p, -1)  # the next correct call is unaffected
+    assert _status() == 0 and torch.isfinite(good).all()

@@ -42,7 +42,7 @@ def _worker(rank: int, world: int, port: int, what: str, results) -> None:
                 parts = [torch.empty_like(x) for _ in range(world)]
                 dist.all_gather(parts, x)
                 want = torch.stack([p.float() for p in parts]).sum(0)
-                got = peer.all_reduce(x)
+                got = peer.all_reduce(x).clone()
                 worst = max(worst, (got.float() - want).abs().max().item() /
                             max(1.0, want.abs().max().item()))
                 # every rank holds the same bits
