@@ -245,16 +245,10 @@ __device__ __forceinline__ long long kth_index(const Row& r, Shared& s, unsigned
   const long long nchunks = (r.n + kChunk - 1) / kChunk;
   for (long long c = tid; c < nchunks; c += kThreads) s.chunk_lo[c] = 0u;
   __syncthreads();
-  // matches per chunk of kChunk consecutive entries (thread t owns 4 t .. 4 t + 3 of a chunk)
-  for (long long c = 0; c < nchunks; ++c) {
-    uint32_t cnt = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const long long i = c * kChunk + 4 * tid + j;
-      if (i < r.n && pred(value_of(r, r.x[i]))) ++cnt;
-    }
-    if (cnt) atomicAdd(&s.chunk_lo[c], cnt);
-  }
+  // matches per chunk of kChunk consecutive entries (matches are few: one atomic each)
+  for_each(r, [&](long long i, float x) {
+    if (pred(value_of(r, x))) atomicAdd(&s.chunk_lo[i / kChunk], 1u);
+  });
   __syncthreads();
   if (tid == 0) {
     unsigned long long seen = 0;
@@ -395,19 +389,33 @@ __global__ void __launch_bounds__(kThreads, 1) sample_kernel(const SampleArgs a)
     const long long nchunks = (r.n + kChunk - 1) / kChunk;
     for (long long c = tid; c < nchunks; c += kThreads) s.chunk_hi[c] = s.chunk_lo[c] = 0u;
     __syncthreads();
-    for (long long c = 0; c < nchunks; ++c) {
-      unsigned long long u = 0;
+    // four chunks per trip, their loads in flight together (one CTA streams the row,
+    // so a trip per chunk would be bound by memory latency)
+    for (long long c0 = 0; c0 < nchunks; c0 += 4) {
+      float v[4][4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const long long i = c * kChunk + 4 * tid + j;
-        if (i < r.n) u += to_units(value_of(r, r.x[i]));
+      for (int k = 0; k < 4; ++k) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const long long i = (c0 + k) * kChunk + 4 * tid + j;
+          v[k][j] = i < r.n ? r.x[i] : 0.f;
+        }
       }
-      // per-warp sum first: 32 times fewer atomics
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) u += __shfl_xor_sync(0xffffffffu, u, o);
-      if ((tid & 31) == 0 && u) {
-        atomicAdd(&s.chunk_lo[c], static_cast<uint32_t>(u) & ((1u << kLoBits) - 1u));
-        atomicAdd(&s.chunk_hi[c], static_cast<uint32_t>(u >> kLoBits));
+      for (int k = 0; k < 4; ++k) {
+        unsigned long long u = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const long long i = (c0 + k) * kChunk + 4 * tid + j;
+          if (i < r.n) u += to_units(value_of(r, v[k][j]));
+        }
+        // per-warp sum first: 32 times fewer atomics
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) u += __shfl_xor_sync(0xffffffffu, u, o);
+        if ((tid & 31) == 0 && u && c0 + k < nchunks) {
+          atomicAdd(&s.chunk_lo[c0 + k], static_cast<uint32_t>(u) & ((1u << kLoBits) - 1u));
+          atomicAdd(&s.chunk_hi[c0 + k], static_cast<uint32_t>(u >> kLoBits));
+        }
       }
     }
     __syncthreads();
