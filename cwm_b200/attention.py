@@ -74,7 +74,7 @@ def reset_workspaces() -> None:
 _lib.on_bad_status.append(reset_workspaces)
 
 
-def _paged_attn_impl(
+def _paged_attn_launch(
     query: torch.Tensor,
     key: torch.Tensor,
     value: torch.Tensor,
@@ -85,11 +85,13 @@ def _paged_attn_impl(
     max_seqlen_k: int,
     softmax_scale: float,
     window_left: int,
+    out: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor]:
     total_q, hq, d = query.shape
     num_pages, page_size, hkv, _ = key.shape
     batch = seqused_k.shape[0]
-    out = torch.empty_like(query)
+    if out is None:
+        out = torch.empty_like(query)
     lse = torch.empty((hq, total_q), dtype=torch.float32, device=query.device)
     if total_q == 0 or batch == 0:
         return out, lse
@@ -104,6 +106,22 @@ def _paged_attn_impl(
         )
     _lib.check(code, "mha_fwd")
     return out, lse
+
+
+def _paged_attn_impl(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    seqused_k: torch.Tensor,
+    block_table: torch.Tensor,
+    max_seqlen_q: int,
+    max_seqlen_k: int,
+    softmax_scale: float,
+    window_left: int,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    return _paged_attn_launch(query, key, value, cu_seqlens_q, seqused_k, block_table,
+                              max_seqlen_q, max_seqlen_k, softmax_scale, window_left)
 
 
 _paged_attn_op = torch.library.custom_op(
@@ -134,6 +152,7 @@ def mha_fwd(
     is_causal: bool = True,
     window_left: int = -1,
     window_right: int = -1,
+    out: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor]:
     """Variable-length paged grouped-query attention forward.
 
@@ -154,6 +173,11 @@ def mha_fwd(
 
     Only what the reference uses is built: ``cu_seqlens_k`` and ``leftpad_k`` must
     be None, ``p`` 0, ``is_causal`` True and ``window_right`` -1 or 0.
+
+    ``out`` (not in the reference's signature): where to write the result instead
+    of a new tensor; contiguous, shaped and typed like ``query``, on the device or in
+    pinned host memory (the kernels then store the rows straight across the host
+    link, which saves the separate device-to-host copy of a step's output).
 
     Returns ``(out, lse)`` with ``out`` like ``query`` and ``lse`` float32
     ``(Hq, T)``.
@@ -202,6 +226,14 @@ def mha_fwd(
     _require_cuda("mha_fwd", query, key, value, cu_seqlens_q, seqused_k, block_table)
     # never read past the block table, whatever bound the caller gave
     max_k = min(int(max_seqlen_k), block_table.shape[1] * page_size)
+    if out is not None:
+        if (out.shape != query.shape or out.dtype != query.dtype or not out.is_contiguous()
+                or not (out.is_cuda or out.is_pinned())):
+            raise ValueError("out must be contiguous, shaped and typed like query, and live on "
+                             "the device or in pinned host memory")
+        return _paged_attn_launch(query, key, value, cu_seqlens_q, seqused_k, block_table,
+                                  int(max_seqlen_q), max_k, float(softmax_scale),
+                                  int(window_left), out)
     return (_paged_attn_op if _use_registered_op() else _paged_attn_impl)(
         query, key, value, cu_seqlens_q, seqused_k, block_table, int(max_seqlen_q), max_k,
         float(softmax_scale), int(window_left),
@@ -326,7 +358,9 @@ def qkv_rope_kv_write(
     heads]`` (any row stride).  Returns the rotated queries ``(T, Hq, D)``; the
     rotated keys and the values go straight to their pages, ``qkv`` is only read.
     Same positions, block table and ``batch_size`` rule as ``rope_kv_write``
-    (``cwm/fastgen/forward.py:608-632``)."""
+    (``cwm/fastgen/forward.py:608-632``).  ``qkv`` may also live in pinned host
+    memory: the kernel then reads the rows straight across the host link, which
+    saves the separate host-to-device copy of a step's inputs."""
     if qkv.ndim != 2 or qkv.stride(1) != 1:
         raise ValueError("qkv must be 2-D (T, (Hq + 2 Hkv) * D) with unit stride in its last dimension")
     t, width = qkv.shape
@@ -356,17 +390,20 @@ def qkv_rope_kv_write(
             raise ValueError("batch_size must be a 0-d int32 or int64 tensor")
         if src_batch is not None:
             raise ValueError("src_batch and batch_size cannot be given together")
-    _require_cuda("qkv_rope_kv_write", qkv, cache_k, cache_v, pos, freqs, page_tbl, src_batch,
+    if not qkv.is_cuda and not qkv.is_pinned():
+        raise RuntimeError("qkv_rope_kv_write: qkv must live on a CUDA device or in pinned host "
+                           "memory")
+    _require_cuda("qkv_rope_kv_write", cache_k, cache_v, pos, freqs, page_tbl, src_batch,
                   batch_size)
-    q_out = torch.empty((t, n_heads, d), dtype=qkv.dtype, device=qkv.device)
-    with _on_device(qkv):
+    q_out = torch.empty((t, n_heads, d), dtype=qkv.dtype, device=cache_k.device)
+    with _on_device(cache_k):
         code = _lib.load().cwm_qkv_rope_kv_write(
             qkv.data_ptr(), qkv.stride(0) if t > 1 else width, q_out.data_ptr(),
             cache_k.data_ptr(), cache_v.data_ptr(), pos.data_ptr(), freqs.data_ptr(),
             page_tbl.data_ptr(), _ptr(src_batch), _ptr(batch_size),
             int(batch_size is not None and batch_size.dtype == torch.int64), t, n_heads,
             n_kv_heads, d, _DTYPES[qkv.dtype], page_size, page_tbl.stride(0), page_tbl.shape[1],
-            cache_k.stride(0), cache_k.shape[0], _stream(qkv),
+            cache_k.stride(0), cache_k.shape[0], _stream(cache_k),
         )
     _lib.check(code, "qkv_rope_kv_write")
     return q_out

@@ -178,10 +178,14 @@ def gqa_attention_packed(
     actual_batch_size: torch.Tensor | None,
     freqs: torch.Tensor,
     window_left: int,
+    out: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """``gqa_attention`` for the packed output ``qkv = x @ [wq | wk | wv]^T`` of one
     stacked projection, ``(T, (Hq + 2 Hkv) * D)``: same result as splitting it into
-    ``xq``, ``xk``, ``xv`` and calling ``gqa_attention``, without the copies."""
+    ``xq``, ``xk``, ``xv`` and calling ``gqa_attention``, without the copies.  ``qkv``
+    may live in pinned host memory and ``out`` may name a pinned host tensor for the
+    result: the two kernels then move the step's inputs and outputs across the host
+    link themselves."""
     cache_k, cache_v = cache.cache_kv(layer_idx)
     page = attn_bias.page_size
     d = qkv.shape[1] // (n_heads + 2 * n_kv_heads)
@@ -194,6 +198,6 @@ def gqa_attention_packed(
         xq, cache_k.reshape(-1, page, n_kv_heads, d), cache_v.reshape(-1, page, n_kv_heads, d),
         attn_bias.q_seqinfo.seqstart, None, attn_bias.k_seqinfo.seqlen, None,
         attn_bias.q_seqinfo.max_seqlen, attn_bias.k_seqinfo.max_seqlen, 0,
-        attn_bias.block_tables, d**-0.5, True, window_left, -1,
+        attn_bias.block_tables, d**-0.5, True, window_left, -1, out=out,
     )
     return out

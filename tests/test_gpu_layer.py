@@ -160,3 +160,41 @@ def test_registered_torch_ops_match_the_eager_wrappers(ops):
     out, lse = ops.mha_fwd(p.q, k4, v4, p.cu_seqlens_q, None, p.seqused_k, None, 150, 512, 0,
                            p.block_table, 128**-0.5, True, -1, -1)
     assert torch.equal(out_op, out) and torch.equal(lse_op, lse)
+
+
+def test_packed_layer_with_pinned_host_input_and_output(lib):
+    """The packed layer step with its inputs read from, and its result written to,
+    pinned host memory by the kernels themselves equals the same step on device
+    buffers bit for bit (decode and prefill rows)."""
+    import cwm_b200
+    from cwm_b200.layer import gqa_attention_packed, prefill_positions
+
+    hq, hkv, d, page = 12, 2, 128, 256
+    g = torch.Generator().manual_seed(77)
+    for seq_info in ([(300, 1), (1000, 1), (0, 1), (4000, 1)], [(100, 200), (0, 131)]):
+        q_lens = [n1 for _, n1 in seq_info]
+        kv_lens = [n0 + n1 for n0, n1 in seq_info]
+        cols = max((n + page - 1) // page for n in kv_lens)
+        n_pages = cols * len(seq_info)
+        table = torch.randperm(n_pages, generator=g).reshape(len(seq_info), cols).to(torch.int32).to(DEV)
+        rows0 = torch.randn(n_pages * page, 2 * hkv * d, generator=g).to(torch.bfloat16)
+        t = sum(q_lens)
+        qkv = torch.randn(t, (hq + 2 * hkv) * d, generator=g).to(torch.bfloat16)
+        q_batch, q_pos = prefill_positions(seq_info, DEV)
+        decode = max(q_lens) == 1
+        bias = cwm_b200.AttnBias.from_seqlens(q_lens, kv_lens, table, page)
+        freqs = cwm_b200.rope_freqs(d, 1e6).to(DEV)
+        results = []
+        for pinned in (False, True):
+            cache = cwm_b200.RawCache([rows0.to(DEV)], [hkv * d, hkv * d], n_pages * page)
+            src = qkv.pin_memory() if pinned else qkv.to(DEV)
+            out = torch.zeros(t, hq, d, dtype=torch.bfloat16).pin_memory() if pinned else None
+            got = gqa_attention_packed(src, hq, hkv, cache, 0, bias, q_pos,
+                                       None if decode else q_batch, None, freqs, -1, out=out)
+            torch.cuda.synchronize()
+            if pinned:
+                assert got.data_ptr() == out.data_ptr() and not got.is_cuda
+            results.append((got.cpu().clone(), cache.caches[0].cpu().clone()))
+        assert torch.equal(results[0][0].view(torch.int16), results[1][0].view(torch.int16))
+        assert torch.equal(results[0][1].view(torch.int16), results[1][1].view(torch.int16))
+        assert results[0][0].abs().sum() > 0
