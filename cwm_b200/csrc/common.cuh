@@ -164,6 +164,17 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Per-warpgroup register budget (every warp of an aligned group of four executes
+// the same one): give registers back to the CTA's pool / take them from it.
+template <int kRegs>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
 // Three-input maximum and packed pairs of fp32 operations (sm_100a).
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
