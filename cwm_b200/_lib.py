@@ -68,7 +68,6 @@ SIGNATURES: dict[str, tuple] = {
     "cwm_silu_mul": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "cwm_paged_attn_workspace_bytes": (c_size_t, [c_int, c_int64, c_int, c_int, c_int]),
     "cwm_test_hooks": (c_int, [ctypes.c_longlong, c_int]),
-    "cwm_test_prefill_kernel": (c_int, [c_int]),
     "cwm_sample": (
         c_int,
         [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,

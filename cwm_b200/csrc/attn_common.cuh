@@ -57,10 +57,8 @@ size_t decode_partial_bytes(int max_ctas);
 // Values of the self-test hooks (cwm_test_hooks) for the next launches.
 long long hook_wait_cycles();
 int hook_drop_last_tile();
-int launch_prefill_tc(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap,
-                      AttnArgs a, bool bf16, cudaStream_t stream);
-int launch_prefill_pair(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap,
-                      AttnArgs a, bool bf16, cudaStream_t stream);
+int launch_prefill(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap,
+                   AttnArgs a, bool bf16, cudaStream_t stream);
 
 // mma.sync m16n8k16 where only rows 0..7 of the accumulator are kept: the two
 // values of rows 8..15 go to scratch registers and enter as zero, so that

@@ -57,11 +57,6 @@ int sm_count() {
 namespace {
 std::atomic<long long> g_hook_wait_cycles{kDefaultWaitCycles};
 std::atomic<int> g_hook_drop_last{0};
-std::atomic<int> g_hook_prefill_kernel{0};
-// Chunks whose contexts can reach this many keys go to the kernel that runs as pairs
-// of CTAs; shorter ones to the kernel with two query tiles per CTA, whose fixed cost
-// per query tile is lower (measured cross-over on B200: between 3072 and 4096 keys).
-constexpr long long kPairMinKeys = 4096;
 }  // namespace
 
 long long hook_wait_cycles() { return g_hook_wait_cycles.load(std::memory_order_relaxed); }
@@ -192,15 +187,6 @@ extern "C" int cwm_test_hooks(long long wait_limit_cycles, int drop_last_tile) {
   return CWM_OK;
 }
 
-extern "C" int cwm_test_prefill_kernel(int which) {
-  if (which < 0 || which > 2) {
-    set_error("cwm_test_prefill_kernel: which must be 0 (by size), 1 or 2, got %d", which);
-    return CWM_ERR_INVALID;
-  }
-  g_hook_prefill_kernel.store(which, std::memory_order_relaxed);
-  return CWM_OK;
-}
-
 extern "C" size_t cwm_paged_attn_workspace_bytes(int batch, int64_t total_q, int hq, int hkv,
                                                  int d) {
   (void)total_q;
@@ -318,16 +304,7 @@ extern "C" int cwm_paged_attn_fwd(const void* q, const void* k, const void* v, v
     rc = get_kv_map(q, static_cast<long long>(hq) * d, total_q, static_cast<long long>(hq) * d * 2,
                     dtype, 128, &qmap, false);
     if (rc != CWM_OK) return rc;
-    // max_seqlen_k bounds the contexts of the chunks only if most sequences of the call
-    // are chunks: with many single-query sequences in the same call it is likely to
-    // come from one of those.  (total_q - batch) / (max_seqlen_q - 1) is the least
-    // number of sequences with more than one query.
-    const long long chunks_least = (total_q - batch + max_seqlen_q - 2) / (max_seqlen_q - 1);
-    const int forced = g_hook_prefill_kernel.load(std::memory_order_relaxed);
-    const bool use_pair = forced == 0 ? (max_seqlen_k >= kPairMinKeys && 2 * chunks_least >= batch)
-                                      : forced == 2;
-    rc = use_pair ? launch_prefill_pair(qmap, kmap, vmap, a, bf16, st)
-                  : launch_prefill_tc(qmap, kmap, vmap, a, bf16, st);
+    rc = launch_prefill(qmap, kmap, vmap, a, bf16, st);
     if (rc != CWM_OK) return rc;
   }
   return CWM_OK;

@@ -78,19 +78,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Default limit of a bounded wait, in SM clock cycles (about two seconds).
 constexpr long long kDefaultWaitCycles = 4000000000LL;
 
-// Non-suspending test of an mbarrier phase (returns at once).
-__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-
 // Bounded wait: gives up after `limit` cycles of SM clock, so that a protocol
 // error shows up as a status bit instead of a hung GPU.  Returns false on timeout.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,

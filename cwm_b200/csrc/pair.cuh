@@ -126,37 +126,13 @@ __device__ __forceinline__ Desc2 split_desc(uint64_t d) {
   return Desc2{static_cast<uint32_t>(d), static_cast<uint32_t>(d >> 32)};
 }
 
-// D[tmem, both CTAs] (+)= A[smem, 128 rows per CTA] * B[smem, N/2 columns per CTA].
-__device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
-                                            uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
-                                            uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p, e;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
-      "elect.sync _|e, 0xffffffff;\n\t"
-      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
-      "@e tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
-      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// D[tmem] (+)= A[tmem, 128 rows per CTA] * B[smem, N/2 columns per CTA].
-__device__ __forceinline__ void mma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
-                                            uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p, e;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
-      "elect.sync _|e, 0xffffffff;\n\t"
-      "mov.b64 db, {%2, %3};\n\t"
-      "@e tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
-      "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-
 // The eight K=16 steps of one 128-deep product as a single block: one election, the
 // descriptor start addresses stepped in place.  The issuing warp spends a few
 // instructions per tcgen05.mma instead of an election, a predicate and two 64-bit
 // moves each, which matters because every step keeps the tensor cores busy for only
 // 64 cycles and the warp shares its scheduler with two softmax warps.
 //
+// D[tmem, both CTAs] (+)= A[smem, 128 rows per CTA] * B[smem, N/2 columns per CTA].
 // A and B tiles are two 64-element halves of the K extent (128-byte swizzled rows);
 // kAHalf / kBHalf = distance between the halves in 16-byte units.  Within a half the
 // K=16 steps are 32 bytes (2 units) apart.
@@ -186,7 +162,7 @@ __device__ __forceinline__ void mma_ss_pair_x8(uint32_t d_tmem, uint32_t a_lo, u
 }
 #undef CWM_SS_NEXT
 
-// The same for D (+)= A[tmem] * B[smem]: A advances by kAStep columns of tensor
+// The same for D[tmem] (+)= A[tmem, 128 rows per CTA] * B[smem, N/2 columns per CTA]: A advances by kAStep columns of tensor
 // memory per step, B by kBStep units of 16 bytes.
 #define CWM_TS_NEXT                                                                    \
   "add.u32 ra, ra, %6;\n\tadd.u32 rb, rb, %7;\n\tmov.b64 db, {rb, %3};\n\t"            \

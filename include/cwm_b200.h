@@ -140,13 +140,6 @@ CWM_API size_t cwm_paged_attn_workspace_bytes(int batch, int64_t total_q, int hq
  * after the call. */
 CWM_API int cwm_test_hooks(long long wait_limit_cycles, int drop_last_tile);
 
-/* Self-test hook: which of the two chunked-prefill kernels later cwm_paged_attn_fwd
- * calls use.  0 (default): chosen by max_seqlen_k (the kernel that runs as pairs of
- * CTAs sharing every K/V tile from 4096 keys on, the kernel with two query tiles per
- * CTA below); 1: always the latter; 2: always the former.  Both compute the same
- * function; the library's tests run their prefill cases through each. */
-CWM_API int cwm_test_prefill_kernel(int which);
-
 /* Variable-length paged-KV grouped-query attention, causal, with an optional
  * sliding window.  Replaces the call
  *   mha_fwd(query, key, value, cu_seqlens_q, None, seqused_k, None, max_seqlen_q,

@@ -20,17 +20,11 @@ DEV = "cuda:0"
 TOL = 2e-2
 
 
-@pytest.fixture(scope="module", params=["by_size", "two_tiles_per_cta", "cta_pairs"])
-def ops(lib, request):
-    """The package, with the chunked-prefill kernel chosen by size (the product rule)
-    or forced to either of the two kernels, so that every prefill case of this file
-    runs through both."""
+@pytest.fixture(scope="module")
+def ops(lib):
     import cwm_b200
 
-    which = {"by_size": 0, "two_tiles_per_cta": 1, "cta_pairs": 2}[request.param]
-    assert lib.cwm_test_prefill_kernel(which) == 0
-    yield cwm_b200
-    assert lib.cwm_test_prefill_kernel(0) == 0
+    return cwm_b200
 
 
 def _status():

@@ -38,28 +38,16 @@ def _run(p, window_left=-1):
     return out
 
 
-@pytest.mark.parametrize("kind", ["decode", "prefill", "prefill_one_tile", "prefill_cta_pairs",
-                                  "prefill_cta_pairs_one_tile"])
+@pytest.mark.parametrize("kind", ["decode", "prefill", "prefill_one_tile"])
 def test_wait_that_runs_out_sets_status_and_context_survives(lib, kind):
     from cwm_b200 import _lib
 
     if kind == "decode":
         p = make_problem([1, 1], [700, 130], hq=12, hkv=2, seed=21)
-    elif kind in ("prefill", "prefill_cta_pairs"):
+    elif kind == "prefill":
         p = make_problem([300], [400], hq=12, hkv=2, seed=22)
     else:
         p = make_problem([90], [90], hq=12, hkv=2, seed=23)
-    # the kernel that runs as pairs of CTAs is chosen by size in production; force it here
-    assert lib.cwm_test_prefill_kernel(2 if "cta_pairs" in kind else 1) == 0
-    try:
-        _wait_runs_out(lib, p)
-    finally:
-        assert lib.cwm_test_prefill_kernel(0) == 0
-
-
-def _wait_runs_out(lib, p):
-    from cwm_b200 import _lib
-
     stream = torch.cuda.current_stream().cuda_stream
     good = _run(p)
     assert _lib.device_status(stream) == 0
