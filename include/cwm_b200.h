@@ -162,10 +162,11 @@ CWM_API int cwm_test_hooks(long long wait_limit_cycles, int drop_last_tile);
  * Limits (CWM_ERR_UNSUPPORTED otherwise): d == 128; bf16 or fp16; hq / hkv <= 8;
  * page_size a multiple of 64; num_pages * page_size < 2^31; batch up to about
  * 1300 sequences (the schedulers keep one int per sequence in shared memory).
- * max_seqlen_q must be at least the true maximum of the query counts: the launch
- * grid is sized from it, and when total_q == batch * max_seqlen_q > batch the
- * decode kernel is not launched at all.  A call whose lengths break this promise
- * computes only part of the output and sets status bit 4.  Keys at or beyond
+ * max_seqlen_q must be at least the true maximum of the query counts: when
+ * total_q == batch * max_seqlen_q > batch the decode kernel is not launched at
+ * all, and the prefill kernel checks the number of query blocks against it.  A
+ * call whose lengths break this promise sets status bit 4 and may have computed
+ * only part of the output.  Keys at or beyond
  * seqused_k[b] are never used by the decode kernel, whatever their pages hold;
  * the prefill kernel multiplies the V rows of masked keys of a partly used tile
  * by zero, so the cache pages it touches must hold finite values (a cache that
