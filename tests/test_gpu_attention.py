@@ -315,6 +315,45 @@ def test_randomized_problems(ops):
         _check(ops, p, window)
 
 
+def test_prefill_many_items_per_cluster(ops):
+    """More work items than the persistent grid has clusters, of very different
+    lengths, so that every cluster walks several items and its rings, score slots and
+    barrier phases run on from one item to the next (odd and even tile counts, one-tile
+    items, items whose queries see no key at all in between)."""
+    g = torch.Generator().manual_seed(77)
+    q_lens, kv = [], []
+    for i in range(40):
+        t = int(torch.randint(2, 300, (1,), generator=g))
+        kind = i % 5
+        if kind == 0:
+            n = t  # no cached prefix
+        elif kind == 1:
+            n = t + int(torch.randint(1, 2500, (1,), generator=g))
+        elif kind == 2:
+            n = max(0, t - 130)  # the first queries sit before position 0
+        elif kind == 3:
+            n = 0  # no key at all: every work item of the sequence is empty
+        else:
+            n = t + 128 * int(torch.randint(0, 6, (1,), generator=g))
+        q_lens.append(t)
+        kv.append(n)
+    for hq, hkv in ((12, 2), (3, 1)):
+        p = make_problem(q_lens, kv, hq=hq, hkv=hkv, seed=770 + hq)
+        _check(ops, p, -1)
+        _check(ops, p, 300)
+
+
+def test_prefill_long_item_lists_are_deterministic(ops):
+    """Two runs over a long item list give the same bits (tile-to-group assignment and
+    buffer reuse depend only on the list, not on timing)."""
+    p = make_problem([700, 64, 1000, 129, 2, 513], [700 + 3000, 64, 1000 + 100, 129 + 900, 2, 513],
+                     hq=12, hkv=2, seed=78)
+    a, _ = _run(ops, p, 1023)
+    b, _ = _run(ops, p, 1023)
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    _check(ops, p, 1023)
+
+
 def test_decode_never_uses_rows_beyond_the_context(ops):
     """Rows of the last page at or beyond ``seqused_k`` hold whatever the page held
     before; filled with NaN and Inf they must not change a bit of the decode output
@@ -339,8 +378,8 @@ def test_decode_never_uses_rows_beyond_the_context(ops):
 
 
 def test_too_small_max_seqlen_q_is_reported(ops):
-    """The prefill grid is sized from max_seqlen_q; a caller that understates it gets
-    status bit 4 (part of the output was not computed) instead of silence."""
+    """max_seqlen_q is a promise of the caller; one that understates it gets status
+    bit 4 instead of silence."""
     p = make_problem([300, 40], [300, 500], hq=12, hkv=2, seed=92)
     pg = p.to(DEV)
     k4, v4 = pg.kv_views()
