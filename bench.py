@@ -529,8 +529,13 @@ def run_decode(args, rank, local_rank, n_gpus, dist, workload, window_left, with
             dist.barrier()
             torch.cuda.synchronize()
 
-    # The reference engine replays decode from CUDA graphs (generate.py:338-373); so
-    # does the timed region: one captured step, replayed K times.
+    # The reference engine replays decode from CUDA graphs (generate.py:338-373), one
+    # graph holding the attention calls of all layers of a decode step one after
+    # another.  So does the timed region: a graph of `per_graph` steps (a divisor of K,
+    # at most 10: ten layers' worth), replayed K / per_graph times.  Inside a graph a
+    # launch may become resident while the one before drains (programmatic stream
+    # serialization), as it does between the kernels of the reference's decode graph.
+    per_graph = max(g for g in range(1, 11) if args.steps % g == 0)
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
@@ -540,7 +545,10 @@ def run_decode(args, rank, local_rank, n_gpus, dist, workload, window_left, with
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
         graph_out, _ = attn_step()
-    for _ in range(max(3, args.warmup)):
+        graph_last = graph_out
+        for _ in range(per_graph - 1):
+            graph_last, _ = attn_step()
+    for _ in range(max(3, -(-args.warmup // per_graph))):
         graph.replay()
     sync_all()
 
@@ -549,7 +557,10 @@ def run_decode(args, rank, local_rank, n_gpus, dist, workload, window_left, with
     order = sorted(range(batch), key=lambda b: kv_lens[b])
     sampled = [order[0], order[batch // 2], order[-1]]
     want = _oracle_decode_rows(row, table, kv_lens, xq, hq_l, hkv_l, window_left, sampled)
-    max_abs = max((graph_out[b].cpu().float() - want[b]).abs().max().item() for b in sampled)
+    max_abs = max((o[b].cpu().float() - want[b]).abs().max().item()
+                  for b in sampled for o in (graph_out, graph_last))
+    if not torch.equal(graph_out.view(torch.int16), graph_last.view(torch.int16)):
+        raise SystemExit("the first and the last step of the captured graph differ")
     par = torch.tensor([max_abs], device=dev)
     if dist is not None:
         dist.all_reduce(par, op=dist.ReduceOp.MAX)
@@ -564,7 +575,7 @@ def run_decode(args, rank, local_rank, n_gpus, dist, workload, window_left, with
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             sync_all()
             t0.record()
-            for _ in range(args.steps):
+            for _ in range(args.steps // per_graph):
                 graph.replay()
             t1.record()
             sync_all()
@@ -606,8 +617,10 @@ def run_decode(args, rank, local_rank, n_gpus, dist, workload, window_left, with
         "arm_note": {"heads_per_gpu": f"{hq_l}q/{hkv_l}kv", "kv_bytes_per_gpu": bytes_rank,
                      **({"as_shard": f"one GPU running the share of 1 of {args.as_shard} ranks"}
                         if args.as_shard > 1 else {}),
-                     "launch": "one captured CUDA-graph step replayed per step; the timed "
-                               f"region is run {args.repeats} times, ms_per_step is the median",
+                     "launch": f"CUDA graphs of {per_graph} consecutive steps (as the layers of "
+                               f"a decode graph follow one another), {args.steps // per_graph} "
+                               f"replays = {args.steps} steps per timed region; the region is "
+                               f"run {args.repeats} times, ms_per_step is the median",
                      "l2": "inputs larger than L2" if bytes_rank > 2 * L2_BYTES else
                            "inputs not larger than L2 at this sharding",
                      "parallelism": f"tp{n_gpus}"},
@@ -620,11 +633,11 @@ def run_decode(args, rank, local_rank, n_gpus, dist, workload, window_left, with
                      "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                      "traffic": int(bytes_rank * DECODE_TRAFFIC_RATIO),
                      "peak_kind": f"of {peak_kind}",
-                     "note": "per GPU; events bracket the decode kernel (split-KV merge "
+                     "note": "per GPU; events bracket the decode kernels (split-KV merge "
                              "included, one launch per step); traffic is the ncu DRAM "
                              "read+write of a smaller capture scaled by the algorithmic bytes"},
     }
-    del graph, graph_out
+    del graph, graph_out, graph_last
 
     # -------------------------------------------------- end to end, host buffers
     if with_e2e:

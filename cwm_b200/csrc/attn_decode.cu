@@ -326,14 +326,20 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
         const int slot = seg_start <= g_begin ? 0 : 1;
         frag_store(f, a.partial + (static_cast<long long>(blockIdx.x) * 2 + slot) * kPartialFloats,
                    lane);
-        __threadfence();  // the partial is visible device-wide before the arrival counts
+        // The warp's stores are ordered before lane 0's arrival by the warp barrier, and
+        // the arrival is a release (the partial is visible device-wide before it counts)
+        // and an acquire (the CTA that arrives last sees every earlier partial): one
+        // atomic instead of a fence on either side of it.
         __syncwarp();
         if (lane == 0) {
           int* counter = a.counters + b * a.hkv + h;
-          const int arrived = atomicAdd(counter, 1);
+          int arrived;
+          asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;"
+                       : "=r"(arrived)
+                       : "l"(counter)
+                       : "memory");
           const int last = arrived == c_last - c_first ? 1 : 0;
           if (last) *counter = 0;  // every CTA of the segment has arrived: ready for the next launch
-          __threadfence();
           merge_flag = last;
         }
       }
@@ -343,28 +349,55 @@ decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ 
     if (merge_flag == 0) return;
     // This CTA arrived last: merge the partials of CTAs c_first .. c_last in that
     // order.  Warp w owns output columns 32 w .. 32 w + 31 of every head.  Two passes
-    // with independent loads (the maxima, then the weighted sums), past L1.
+    // (the maxima, then the weighted sums), past L1, each with the loads of up to
+    // kMergeBatch CTAs in flight together: the merge of the last segment is the end
+    // of the kernel, so its latency counts in full.
     auto partial_of = [&](int cta) {
       const int slot = seg_start <= cta * per ? 0 : 1;
       return a.partial + (static_cast<long long>(cta) * 2 + slot) * kPartialFloats;
     };
+    constexpr int kMergeBatch = 8;
     float m = -INFINITY;
-#pragma unroll 4
-    for (int cta = c_first; cta <= c_last; ++cta) m = fmaxf(m, __ldcg(partial_of(cta) + 32 * 32 + lane));
+    for (int c0 = c_first; c0 <= c_last; c0 += kMergeBatch) {
+      float mv[kMergeBatch];
+#pragma unroll
+      for (int k = 0; k < kMergeBatch; ++k) {
+        mv[k] = c0 + k <= c_last ? __ldcg(partial_of(c0 + k) + 32 * 32 + lane) : -INFINITY;
+      }
+#pragma unroll
+      for (int k = 0; k < kMergeBatch; ++k) m = fmaxf(m, mv[k]);
+    }
     const float mu = m == -INFINITY ? 0.f : m;
     float l = 0.f;
     float o[4][2];
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[j][0] = o[j][1] = 0.f;
-#pragma unroll 4
-    for (int cta = c_first; cta <= c_last; ++cta) {
-      const float* buf = partial_of(cta);
-      const float w = fast_exp2(__ldcg(buf + 32 * 32 + lane) - mu);
-      l = fmaf(__ldcg(buf + 33 * 32 + lane), w, l);
+    for (int c0 = c_first; c0 <= c_last; c0 += kMergeBatch) {
+      float mv[kMergeBatch], lv[kMergeBatch], ov[kMergeBatch][4][2];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        o[j][0] = fmaf(__ldcg(buf + (2 * (4 * warp + j)) * 32 + lane), w, o[j][0]);
-        o[j][1] = fmaf(__ldcg(buf + (2 * (4 * warp + j) + 1) * 32 + lane), w, o[j][1]);
+      for (int k = 0; k < kMergeBatch; ++k) {
+        const bool in = c0 + k <= c_last;
+        const float* buf = partial_of(in ? c0 + k : c_last);
+        mv[k] = in ? __ldcg(buf + 32 * 32 + lane) : -INFINITY;
+        lv[k] = in ? __ldcg(buf + 33 * 32 + lane) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          ov[k][j][0] = in ? __ldcg(buf + (2 * (4 * warp + j)) * 32 + lane) : 0.f;
+          ov[k][j][1] = in ? __ldcg(buf + (2 * (4 * warp + j) + 1) * 32 + lane) : 0.f;
+        }
+      }
+      // accumulated in CTA order, as before
+#pragma unroll
+      for (int k = 0; k < kMergeBatch; ++k) {
+        if (c0 + k <= c_last) {
+          const float w = fast_exp2(mv[k] - mu);
+          l = fmaf(lv[k], w, l);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            o[j][0] = fmaf(ov[k][j][0], w, o[j][0]);
+            o[j][1] = fmaf(ov[k][j][1], w, o[j][1]);
+          }
+        }
       }
     }
     const float inv = l > 0.f ? 1.f / l : 0.f;
