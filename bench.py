@@ -328,6 +328,9 @@ def main() -> None:
     ap.add_argument("--all-reduce", default="nccl", choices=["nccl", "peer"],
                     help="decoder workload: the process group's all-reduce, or this package's "
                          "peer-memory kernel for the row-parallel sums")
+    ap.add_argument("--unfused-all-reduce", action="store_true",
+                    help="decoder workload with --all-reduce peer: all-reduce, residual add and "
+                         "RMSNorm as three kernels instead of one")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--as-shard", type=int, default=1,
@@ -445,9 +448,22 @@ def main() -> None:
                         "setup_s": dec["setup_s"], "config": dec["config"],
                         "all_reduce": dec.get("all_reduce")}
 
+            # peer-memory all-reduce fused with the residual add and the norm; if its
+            # check against the oracle fails, the line says so and carries the unfused run
             args.all_reduce = "peer"
-            line["decoder"] = summary(run_decoder(args, rank, local_rank, world, dist, steps=20,
-                                                  with_cpu=False))
+            try:
+                line["decoder"] = summary(run_decoder(args, rank, local_rank, world, dist,
+                                                      steps=20, with_cpu=False))
+            except DecoderParityError as exc:
+                line["decoder_fused_failed"] = str(exc)
+                args.unfused_all_reduce = True
+                line["decoder"] = summary(run_decoder(args, rank, local_rank, world, dist,
+                                                      steps=20, with_cpu=False))
+            if not args.unfused_all_reduce:
+                args.unfused_all_reduce = True
+                line["decoder_unfused"] = summary(run_decoder(args, rank, local_rank, world, dist,
+                                                              steps=20, with_cpu=False))
+            args.unfused_all_reduce = False
             args.all_reduce = "nccl"
             line["decoder_nccl"] = summary(run_decoder(args, rank, local_rank, world, dist,
                                                        steps=20, with_cpu=False))
@@ -878,7 +894,7 @@ def _gather_cat(t: torch.Tensor, dim: int, world: int, dist) -> torch.Tensor:
 
 
 def decoder_parity(margs, rank: int, world: int, dev, dist, ctx: int, collectives: bool,
-                   peer: bool = False) -> dict:
+                   peer: bool = False, fuse: bool = True) -> dict:
     """One decode step of a two-layer model with the real layer shapes (and a small
     vocabulary), tensor-parallel over the same ranks, against the CPU oracle of the
     unsharded model built from the gathered weights and caches: checks sharding,
@@ -891,8 +907,12 @@ def decoder_parity(margs, rank: int, world: int, dev, dist, ctx: int, collective
     small = dataclasses.replace(margs, n_layers=2, vocab_size=8192)
     shard_of = world if collectives else 1
     model = ShardedDecoder(small, rank if collectives else 0, shard_of, dev, seed=7,
-                           peer_all_reduce=peer and collectives and world > 1)
-    batch = 2
+                           peer_all_reduce=peer and collectives and world > 1,
+                           fuse_all_reduce=fuse)
+    # a batch that splits over the ranks, so that the check runs the same all-reduce path
+    # (fused with the residual add and the norm when the peer kernel is used) as the
+    # timed model
+    batch = max(2, shard_of)
     cols = (ctx + 2 + PAGE - 1) // PAGE
     n_pages = batch * cols
     cache = model.build_cache(n_pages * PAGE)
@@ -902,7 +922,8 @@ def decoder_parity(margs, rank: int, world: int, dev, dist, ctx: int, collective
     g = torch.Generator().manual_seed(71)
     table = torch.randperm(n_pages, generator=g).reshape(batch, cols).to(torch.int32)
     tokens = torch.randint(0, small.vocab_size, (batch,), generator=g, dtype=torch.int32)
-    seqlen = torch.tensor([ctx + 1, ctx // 3 + 1], dtype=torch.int32)
+    seqlen = torch.tensor([ctx + 1, ctx // 3 + 1] + [ctx // (i + 2) + 1 for i in range(2, batch)],
+                          dtype=torch.int32)
     before = [c.clone() for c in cache.caches]
     state = DecodeState(batch, table.to(dev), PAGE, dev)
     state.copy_inputs(state.blktbl, tokens.to(dev), seqlen.to(dev))
@@ -945,16 +966,27 @@ def decoder_parity(margs, rank: int, world: int, dev, dist, ctx: int, collective
         scale = want.abs().max().item()
         result = {"max_abs": err, "logit_scale": scale, "tolerance": 3e-2 * scale,
                   "against": "CPU oracle decode step of the unsharded two-layer model (real layer "
-                             f"shapes, vocabulary 8192, contexts {ctx + 1} and {ctx // 3 + 1}) built "
+                             f"shapes, vocabulary 8192, {batch} contexts from {ctx + 1} down) built "
                              "from the gathered weights and cache rows; logits of rank 0"}
         if not err <= 3e-2 * scale:
-            raise SystemExit(f"decoder parity check failed: max-abs {err} vs scale {scale}")
+            result["failed"] = f"decoder parity check failed: max-abs {err} vs scale {scale}"
+    # every rank learns the outcome, so that all of them leave (or go on) together
+    flag = torch.tensor([1 if "failed" in result else 0], device=dev)
+    if dist is not None and collectives:
+        dist.broadcast(flag, src=0)
     if model.coll is not None:
         torch.cuda.synchronize()
         model.coll.close()
     del model, cache, before, full_caches, layers, emb, out_w
     torch.cuda.empty_cache()
+    if int(flag.item()):
+        raise DecoderParityError(result.get("failed", "decoder parity check failed on rank 0"))
     return result
+
+
+class DecoderParityError(SystemExit):
+    """The tensor-parallel decode step disagreed with the CPU oracle; raised on every
+    rank after the peer buffers of the checked model were released."""
 
 
 def run_decoder(args, rank: int, local_rank: int, world: int, dist, steps: int,
@@ -976,7 +1008,8 @@ def run_decoder(args, rank: int, local_rank: int, world: int, dist, steps: int,
             raise SystemExit("--as-shard needs a single process")
         shard_of = args.as_shard
     parity = decoder_parity(margs, rank, world, dev, dist, min(ctx, 16384),
-                            collectives=shard_of == world, peer=args.all_reduce == "peer")
+                            collectives=shard_of == world, peer=args.all_reduce == "peer",
+                            fuse=not args.unfused_all_reduce)
     total_steps = max(3, args.warmup) + steps * args.repeats + 4
     cols = (ctx + total_steps + PAGE - 1) // PAGE
     n_pages = batch * cols
@@ -987,7 +1020,8 @@ def run_decoder(args, rank: int, local_rank: int, world: int, dist, steps: int,
                          f"{free_gb:.0f} GB free: use more GPUs or smaller --decoder-* values")
     model = ShardedDecoder(margs, rank if shard_of == world else 0, shard_of, dev, seed=5,
                            collectives=shard_of == world,
-                           peer_all_reduce=args.all_reduce == "peer" and shard_of == world and world > 1)
+                           peer_all_reduce=args.all_reduce == "peer" and shard_of == world and world > 1,
+                           fuse_all_reduce=not args.unfused_all_reduce)
     cache = model.build_cache(n_pages * PAGE)
     cache.caches[0].normal_()
     for c in cache.caches[1:]:
@@ -1083,8 +1117,12 @@ def run_decoder(args, rank: int, local_rank: int, world: int, dist, steps: int,
                       if shard_of != world else {}),
                    "launch": "one CUDA-graph replay per step", "logits_finite": finite,
                    "sampling": "excluded",
-                   "all_reduce": "peer-memory kernel (cwm_allreduce)" if args.all_reduce == "peer"
-                                 and world > 1 else "process group (NCCL)"},
+                   "all_reduce": ("peer-memory kernel (cwm_allreduce)" if args.unfused_all_reduce
+                                  or batch % world else
+                                  "peer-memory kernel fused with the residual add and the RMSNorm "
+                                  "after it (cwm_allreduce_add_rmsnorm)")
+                                 if args.all_reduce == "peer" and world > 1
+                                 else "process group (NCCL)"},
         "parity": parity, "setup_s": round(setup_s, 1),
         "all_reduce": {"us_per_call": ar_us, "bytes": batch * margs.dim * 2,
                        "calls_per_step": 2 * margs.n_layers + 1,

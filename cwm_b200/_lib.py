@@ -59,6 +59,11 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p],
     ),  # in, scratch table, result table, flag table, epoch, n, dtype, rank, world, stream
+    "cwm_allreduce_add_rmsnorm": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
+         c_float, c_int, c_int, c_int, c_void_p],
+    ),  # in, h, w, scratch table, result table, flag table, epoch, rows, d, eps, dtype, rank, world, stream
     "cwm_allreduce_flag_ints": (c_int, []),
     "cwm_peer_alloc": (c_int, [c_size_t, ctypes.POINTER(c_void_p), c_void_p]),
     "cwm_peer_open": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),

@@ -24,6 +24,8 @@
 // scratch this rank will push into next.
 #include <string.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace cwm {
@@ -153,6 +155,143 @@ __global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArArgs a) {
   }
 }
 
+
+// ---- all-reduce fused with the residual add and the RMSNorm that follow it ------------
+// In a tensor-parallel decoder layer the reduced product is used once: it is added to
+// the residual stream and the sum is normalised (cwm/fastgen/forward.py:763-772,
+// 782-789).  Rank p reduces whole rows here (rows p * R .. p * R + R - 1 of the
+// message, R = rows / world), so it can do both on the spot: it adds the rounded sum
+// to *its own rows* of the residual stream, normalises them and pushes the normalised
+// rows to every rank.  Only the normalised activations are gathered; the residual
+// stream stays sharded by rows (nothing else reads the other rows).  Roundings and
+// the order of every sum are those of all-reduce, then add, then rmsnorm_kernel in
+// helpers.cu (same thread-to-vector mapping, same reduction), so the result is bit
+// for bit the one of the three separate steps.
+struct ArNormArgs {
+  ArArgs ar;
+  uint4* h;        // local residual stream [rows, d]; rows of this rank's slice are updated
+  const uint4* w;  // [d] norm weight
+  int rows_per_rank;
+  int row_vecs;  // 16-byte vectors per row
+  float inv_d;
+  float eps;
+};
+
+constexpr int kNormMaxVpt = 8;
+
+template <bool kBf16>
+__global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(const ArNormArgs n) {
+  using T = typename std::conditional<kBf16, __nv_bfloat16, __half>::type;
+  const ArArgs& a = n.ar;
+  const int epoch = *a.epoch;
+  const int rv = n.row_vecs;
+  // ---- 1. push rows blockIdx.x, blockIdx.x + gridDim.x, ... of every slice to its owner
+  for (int r = blockIdx.x; r < n.rows_per_rank; r += gridDim.x) {
+    for (int idx = threadIdx.x; idx < rv; idx += blockDim.x) {
+      uint4 v[kArMaxWorld];
+#pragma unroll
+      for (int p = 0; p < kArMaxWorld; ++p) {
+        if (p < a.world) {
+          v[p] = a.in[(static_cast<long long>(p) * n.rows_per_rank + r) * rv + idx];
+        }
+      }
+#pragma unroll
+      for (int p = 0; p < kArMaxWorld; ++p) {
+        if (p < a.world) {
+          a.scratch[p][(static_cast<long long>(a.rank) * n.rows_per_rank + r) * rv + idx] = v[p];
+        }
+      }
+    }
+  }
+  bool ok = flag_round(a, 0, epoch);
+  // ---- 2. my rows: sum over the senders in rank order, add to the residual stream,
+  // normalise, push the normalised rows everywhere
+  if (ok) {
+    __shared__ float warp_sums[32];
+    __shared__ float rstd_s;
+    const uint4* mine = a.scratch[a.rank];
+    for (int r = blockIdx.x; r < n.rows_per_rank; r += gridDim.x) {
+      const long long grow = static_cast<long long>(a.rank) * n.rows_per_rank + r;
+      uint4 regs[kNormMaxVpt];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < kNormMaxVpt; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        if (idx < rv) {
+          uint4 v[kArMaxWorld];
+#pragma unroll
+          for (int p = 0; p < kArMaxWorld; ++p) {
+            if (p < a.world) v[p] = mine[(static_cast<long long>(p) * n.rows_per_rank + r) * rv + idx];
+          }
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int p = 0; p < kArMaxWorld; ++p) {
+            if (p < a.world) accumulate<kBf16>(acc, v[p]);
+          }
+          uint4 d;  // the all-reduce result, rounded to the storage type
+          d.x = pack2<kBf16>(acc[0], acc[1]);
+          d.y = pack2<kBf16>(acc[2], acc[3]);
+          d.z = pack2<kBf16>(acc[4], acc[5]);
+          d.w = pack2<kBf16>(acc[6], acc[7]);
+          regs[i] = n.h[grow * rv + idx];
+          T* e = reinterpret_cast<T*>(&regs[i]);
+          const T* de = reinterpret_cast<const T*>(&d);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) e[j] = from_f32<T>(__fadd_rn(to_f32(e[j]), to_f32(de[j])));
+          n.h[grow * rv + idx] = regs[i];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float x = to_f32(e[j]);
+            ss = fmaf(x, x, ss);
+          }
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      __syncthreads();  // warp_sums and rstd_s of the row before are no longer read
+      if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      if (threadIdx.x < 32) {
+        float t = threadIdx.x < (blockDim.x >> 5) ? warp_sums[threadIdx.x] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (threadIdx.x == 0) rstd_s = rsqrtf(t * n.inv_d + n.eps);
+      }
+      __syncthreads();
+      const float rstd = rstd_s;
+#pragma unroll
+      for (int i = 0; i < kNormMaxVpt; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        if (idx < rv) {
+          const uint4 wv = n.w[idx];
+          const T* we = reinterpret_cast<const T*>(&wv);
+          T* e = reinterpret_cast<T*>(&regs[i]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            e[j] = from_f32<T>(__fmul_rn(__fmul_rn(to_f32(e[j]), rstd), to_f32(we[j])));
+          }
+#pragma unroll
+          for (int p = 0; p < kArMaxWorld; ++p) {
+            if (p < a.world) a.result[p][grow * rv + idx] = regs[i];
+          }
+        }
+      }
+    }
+    // ---- 3. my result buffer is complete when every rank's rows have landed
+    ok = flag_round(a, 1, epoch);
+  }
+  if (!ok && threadIdx.x == 0) atomicOr(a.status, DEV_WAIT_TIMEOUT);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int done = atomicAdd(a.epoch + 1, 1);
+    if (done == static_cast<int>(gridDim.x) - 1) {
+      a.epoch[1] = 0;
+      a.epoch[0] = epoch + 1;
+    }
+  }
+}
+
 }  // namespace
 }  // namespace cwm
 
@@ -219,6 +358,74 @@ extern "C" int cwm_allreduce(const void* in, const uint64_t* scratch_ptrs,
     allreduce_kernel<true><<<ctas, kArThreads, 0, st>>>(a);
   } else {
     allreduce_kernel<false><<<ctas, kArThreads, 0, st>>>(a);
+  }
+  CWM_CUDA_CHECK(cudaGetLastError());
+  return CWM_OK;
+}
+
+extern "C" int cwm_allreduce_add_rmsnorm(const void* in, void* h, const void* w,
+                                         const uint64_t* scratch_ptrs, const uint64_t* result_ptrs,
+                                         const uint64_t* flag_ptrs, int32_t* epoch, int64_t rows,
+                                         int d, float eps, int dtype, int rank, int world,
+                                         void* stream) {
+  if (rows == 0) return CWM_OK;
+  if (!in || !h || !w || !scratch_ptrs || !result_ptrs || !flag_ptrs || !epoch) {
+    set_error("allreduce_add_rmsnorm: null pointer");
+    return CWM_ERR_INVALID;
+  }
+  if (world < 1 || world > kArMaxWorld || rank < 0 || rank >= world || rows < 0 || d <= 0) {
+    set_error("allreduce_add_rmsnorm: bad rank / world (at most %d ranks) or shape", kArMaxWorld);
+    return CWM_ERR_INVALID;
+  }
+  if (dtype != CWM_BF16 && dtype != CWM_F16) {
+    set_error("allreduce_add_rmsnorm: bf16 and fp16 only");
+    return CWM_ERR_UNSUPPORTED;
+  }
+  const int row_vecs = d / 8;
+  const int threads = row_vecs >= 512 ? 256 : 128;  // as rmsnorm_kernel, for the same sums
+  if (rows % world != 0 || d % 8 != 0 || row_vecs > threads * kNormMaxVpt ||
+      reinterpret_cast<uintptr_t>(in) % 16 != 0 || reinterpret_cast<uintptr_t>(h) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(w) % 16 != 0) {
+    set_error("allreduce_add_rmsnorm: %lld rows must split evenly over %d ranks, rows must be "
+              "16-byte multiples of at most 32 KiB, tensors 16-byte aligned",
+              static_cast<long long>(rows), world);
+    return CWM_ERR_UNSUPPORTED;
+  }
+  ArNormArgs n;
+  memset(&n, 0, sizeof(n));
+  ArArgs& a = n.ar;
+  for (int p = 0; p < world; ++p) {
+    if (scratch_ptrs[p] % 16 || result_ptrs[p] % 16 || flag_ptrs[p] % 4 || !scratch_ptrs[p] ||
+        !result_ptrs[p] || !flag_ptrs[p]) {
+      set_error("allreduce_add_rmsnorm: peer buffer %d is null or misaligned", p);
+      return CWM_ERR_INVALID;
+    }
+    a.scratch[p] = reinterpret_cast<uint4*>(scratch_ptrs[p]);
+    a.result[p] = reinterpret_cast<uint4*>(result_ptrs[p]);
+    a.flags[p] = reinterpret_cast<int*>(flag_ptrs[p]);
+  }
+  a.in = static_cast<const uint4*>(in);
+  a.epoch = epoch;
+  a.status = status_word();
+  if (a.status == nullptr) {
+    set_error("allreduce_add_rmsnorm: cannot resolve the device status word");
+    return CWM_ERR_CUDA;
+  }
+  a.rank = rank;
+  a.world = world;
+  n.rows_per_rank = static_cast<int>(rows / world);
+  a.slice_vecs = static_cast<long long>(n.rows_per_rank) * row_vecs;
+  n.row_vecs = row_vecs;
+  n.h = static_cast<uint4*>(h);
+  n.w = static_cast<const uint4*>(w);
+  n.inv_d = 1.0f / static_cast<float>(d);
+  n.eps = eps;
+  const int ctas = n.rows_per_rank < kArMaxCtas ? n.rows_per_rank : kArMaxCtas;
+  auto st = static_cast<cudaStream_t>(stream);
+  if (dtype == CWM_BF16) {
+    allreduce_add_rmsnorm_kernel<true><<<ctas, threads, 0, st>>>(n);
+  } else {
+    allreduce_add_rmsnorm_kernel<false><<<ctas, threads, 0, st>>>(n);
   }
   CWM_CUDA_CHECK(cudaGetLastError());
   return CWM_OK;

@@ -93,19 +93,6 @@ int launch_paged_memcpy(const void* src, void* dst, const int32_t* page_tbl,
 }
 
 // ------------------------------------------------------------------------ rope
-__device__ __forceinline__ float to_f32(float v) { return v; }
-__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
-__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
-template <typename T>
-__device__ __forceinline__ T from_f32(float v);
-template <>
-__device__ __forceinline__ float from_f32<float>(float v) { return v; }
-template <>
-__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
-  return __float2bfloat16_rn(v);
-}
-template <>
-__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 
 // Rotates the kElems/2 pairs held in one 16-byte vector.  cs holds (cos, sin)
 // per pair.  Formula of cwm/fastgen/kernels/rope.py:84-85.

@@ -96,12 +96,14 @@ class ShardedDecoder:
     def __init__(self, args: DecoderArgs, rank: int, world: int, device: torch.device,
                  dtype: torch.dtype = torch.bfloat16, seed: int = 0, std: float = 0.02,
                  group: dist.ProcessGroup | None = None, collectives: bool = True,
-                 peer_all_reduce: bool = False) -> None:
+                 peer_all_reduce: bool = False, fuse_all_reduce: bool = True) -> None:
         """``collectives=False`` builds the shard of ``rank`` without a process group
         and skips the all-reduces and the logits gather: the per-GPU work of a
         ``world``-way run on a single GPU, for profiling.  ``peer_all_reduce`` sends
         the row-parallel sums through this package's peer-memory kernel instead of
-        the process group's all-reduce (all ranks on one node)."""
+        the process group's all-reduce (all ranks on one node); with it,
+        ``fuse_all_reduce`` lets passes whose token count divides by the group size run
+        each all-reduce, the residual add and the RMSNorm after it as one kernel."""
         if args.ffn_dim % world or args.vocab_size % world:
             raise ValueError("ffn_dim and vocab_size must be divisible by the group size")
         self.args = args
@@ -109,6 +111,7 @@ class ShardedDecoder:
         self.device, self.dtype = device, dtype
         self.shard: HeadShard = shard_heads(rank, world, args.n_heads, args.n_kv_heads)
         self.coll = None
+        self.fuse_all_reduce = fuse_all_reduce
         if world > 1 and collectives:
             from .tp import PeerAllReduce
 
@@ -152,11 +155,6 @@ class ShardedDecoder:
     def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         return x if self.coll is None else self.coll.all_reduce(x)
 
-    def _linear_all_reduce(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-        if self.coll is None:
-            return F.linear(x, weight)
-        return self.coll.linear_all_reduce(x, weight)
-
     def _embed(self, tokens: torch.Tensor) -> torch.Tensor:
         """Vocabulary-parallel embedding, ``forward.py:134-167``."""
         local = self.tok_embeddings.shape[0]
@@ -181,7 +179,11 @@ class ShardedDecoder:
         hq, hkv = self.shard.n_q, self.shard.n_kv
         cache.page_in(0)
         h = self._embed(tokens)
-        # every residual add is fused with the normalisation that follows it
+        # every residual add is fused with the normalisation that follows it, and with
+        # the all-reduce before it when the peer-memory kernel serves this shape (one
+        # choice for the whole pass: that kernel keeps only this rank's rows of h current)
+        fused = (self.fuse_all_reduce and self.coll is not None
+                 and self.coll.fuses_add_rmsnorm(h.shape[0], h.shape[1], h.dtype))
         x = rmsnorm(h, self.layers[0]["attention_norm"], a.norm_eps)
         n_layers = len(self.layers)
         for i, layer in enumerate(self.layers):
@@ -190,11 +192,18 @@ class ShardedDecoder:
             qkv = F.linear(x, layer["wqkv"])
             attn = gqa_attention_packed(qkv, hq, hkv, cache, i, bias, q_seqpos, q_batch,
                                         actual_batch_size, self.freqs, layer["window_left"])
-            h_out = self._linear_all_reduce(attn.flatten(1, 2), layer["wo"])
-            x = add_rmsnorm(h, h_out, layer["ffn_norm"], a.norm_eps)
-            h_out = self._linear_all_reduce(silu_mul(F.linear(x, layer["w13"])), layer["w2"])
             next_norm = self.layers[i + 1]["attention_norm"] if i + 1 < n_layers else self.norm
-            x = add_rmsnorm(h, h_out, next_norm, a.norm_eps)
+            if self.coll is None:
+                x = add_rmsnorm(h, F.linear(attn.flatten(1, 2), layer["wo"]), layer["ffn_norm"],
+                                a.norm_eps)
+                x = add_rmsnorm(h, F.linear(silu_mul(F.linear(x, layer["w13"])), layer["w2"]),
+                                next_norm, a.norm_eps)
+            else:
+                x = self.coll.linear_all_reduce_add_rmsnorm(
+                    attn.flatten(1, 2), layer["wo"], h, layer["ffn_norm"], a.norm_eps, fused)
+                x = self.coll.linear_all_reduce_add_rmsnorm(
+                    silu_mul(F.linear(x, layer["w13"])), layer["w2"], h, next_norm, a.norm_eps,
+                    fused)
         if logits_idx is not None:
             x = x[logits_idx]
         logits = F.linear(x, self.output)

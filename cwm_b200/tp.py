@@ -156,6 +156,36 @@ class PeerAllReduce:
         nbytes = x.numel() * x.element_size()
         return self._results[which][:nbytes].view(x.dtype).view(x.shape)
 
+    def supports_add_rmsnorm(self, x: torch.Tensor, h: torch.Tensor, w: torch.Tensor) -> bool:
+        return (x.dim() == 2 and self.supports(x) and x.shape[0] % self.world == 0
+                and h.shape == x.shape and h.dtype == x.dtype and h.is_contiguous()
+                and w.dtype == x.dtype and w.numel() == x.shape[1] and w.is_contiguous()
+                and (x.shape[1] * x.element_size()) % 16 == 0
+                and x.shape[1] * x.element_size() <= 32768
+                and h.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+    def all_reduce_add_rmsnorm(self, x: torch.Tensor, h: torch.Tensor, w: torch.Tensor,
+                               eps: float) -> torch.Tensor:
+        """``rmsnorm(h + all_reduce(x), w)`` in one kernel (``cwm_allreduce_add_rmsnorm``).
+        Updates this rank's rows of ``h`` (rows ``rank * T / world`` onwards) in place
+        and leaves the others alone: the caller keeps the residual stream sharded by
+        rows.  Returns the normalised activations of all rows as a view of a result
+        buffer (valid until the second call after this one)."""
+        from . import _lib
+        from .kernels import _DTYPES, _stream
+
+        if not self.supports_add_rmsnorm(x, h, w):
+            raise ValueError("all_reduce_add_rmsnorm: see PeerAllReduce.supports_add_rmsnorm")
+        which = self._calls & 1
+        self._calls += 1
+        code = _lib.load().cwm_allreduce_add_rmsnorm(
+            x.data_ptr(), h.data_ptr(), w.data_ptr(), self._tables[0], self._tables[1 + which],
+            self._tables[3], self._epoch.data_ptr(), x.shape[0], x.shape[1], float(eps),
+            _DTYPES[x.dtype], self.rank, self.world, _stream(x))
+        _lib.check(code, "allreduce_add_rmsnorm")
+        nbytes = x.numel() * x.element_size()
+        return self._results[which][:nbytes].view(x.dtype).view(x.shape)
+
     def close(self) -> None:
         """Collective: unmap the peers' buffers, barrier, free the own buffers."""
         if not self._own:
@@ -204,6 +234,29 @@ class Collectives:
     def linear_all_reduce(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
         """``all_reduce(F.linear(x, weight))`` (``forward.py:763-768,782-785``)."""
         return self.all_reduce(torch.nn.functional.linear(x, weight))
+
+    def fuses_add_rmsnorm(self, rows: int, dim: int, dtype: torch.dtype) -> bool:
+        """Whether ``linear_all_reduce_add_rmsnorm`` runs as one kernel for products of
+        this shape (then only this rank's rows of the residual stream are kept current)."""
+        return (self.peer is not None and rows % self.tp_size == 0 and rows > 0
+                and dtype in (torch.bfloat16, torch.float16)
+                and (dim * 2) % 16 == 0 and dim * 2 <= 32768
+                and rows * dim * 2 <= self.peer.max_bytes and (rows * dim) % (8 * self.tp_size) == 0)
+
+    def linear_all_reduce_add_rmsnorm(self, x: torch.Tensor, weight: torch.Tensor,
+                                      h: torch.Tensor, w: torch.Tensor, eps: float,
+                                      fused: bool) -> torch.Tensor:
+        """``rms_norm(h + all_reduce(F.linear(x, weight)), w)`` with ``h`` updated in
+        place (``forward.py:763-772,782-789``).  ``fused``: through the peer-memory
+        kernel that does all three (the caller asked ``fuses_add_rmsnorm`` first and
+        keeps to one choice for a whole pass, because the fused form keeps only this
+        rank's rows of ``h`` current)."""
+        from .kernels import add_rmsnorm
+
+        y = torch.nn.functional.linear(x, weight)
+        if fused:
+            return self.peer.all_reduce_add_rmsnorm(y, h, w, eps)
+        return add_rmsnorm(h, self.all_reduce(y), w, eps)
 
     def close(self) -> None:
         if self.peer is not None:

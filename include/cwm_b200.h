@@ -245,6 +245,26 @@ CWM_API int cwm_block_copy(const uint64_t* dst_ptrs, const uint64_t* src_ptrs, i
 CWM_API int cwm_allreduce(const void* in, const uint64_t* scratch_ptrs,
                           const uint64_t* result_ptrs, const uint64_t* flag_ptrs, int32_t* epoch,
                           int64_t n_elems, int dtype, int rank, int world, void* stream);
+
+/* The all-reduce above fused with what a tensor-parallel decoder layer does with its
+ * result: h += sum (rounded to the storage type, as the reference's all_reduce then
+ * add_ give), out = rmsnorm(h) * w.  Replaces
+ *   all_reduce(h_out); h = h + h_out; x = rms_norm(h, w, eps)
+ * of cwm/fastgen/forward.py:763-772 and :782-789 (collectives.py:73-88 for the
+ * all-reduce).  in: [rows, d] local partial product.  Rank p sums rows
+ * p * rows / world .. (p + 1) * rows / world - 1, adds them to THOSE rows of its local
+ * h (the other rows of h are left as they are: with this entry point the residual
+ * stream lives sharded by rows, each rank keeping its own rows current), normalises
+ * them and writes the normalised rows into every rank's result buffer, which then
+ * holds all of out = [rows, d], the same bits on every rank and the same bits as the
+ * three separate calls give.  rows % world == 0; d * element size a multiple of 16
+ * bytes and at most 32 KiB; buffers, epoch, bounded waits and ordering rules as for
+ * cwm_allreduce (scratch and result need rows * d elements). */
+CWM_API int cwm_allreduce_add_rmsnorm(const void* in, void* h, const void* w,
+                                      const uint64_t* scratch_ptrs, const uint64_t* result_ptrs,
+                                      const uint64_t* flag_ptrs, int32_t* epoch, int64_t rows,
+                                      int d, float eps, int dtype, int rank, int world,
+                                      void* stream);
 CWM_API int cwm_allreduce_flag_ints(void);
 CWM_API int cwm_allreduce_ctas(int64_t n_elems, int world);
 

@@ -98,6 +98,77 @@ def _worker(rank: int, world: int, port: int, what: str, results) -> None:
             scale = logits[False].abs().max().item()
             assert (logits[True] - logits[False]).abs().max().item() <= 2e-2 * scale
             assert _lib.device_status(torch.cuda.current_stream().cuda_stream) == 0
+        elif what == "allreduce_add_rmsnorm":
+            from cwm_b200.kernels import add_rmsnorm
+
+            peer = PeerAllReduce(None, dev)
+            g = torch.Generator(device=dev).manual_seed(300 + rank)
+            gw = torch.Generator(device=dev).manual_seed(299)  # the same weights on every rank
+            for it, (rows, d) in enumerate([(128, 6144), (4, 256), (16, 1024), (128, 6144),
+                                            (2, 8192), (256, 512)] * 3):
+                x = torch.randn(rows, d, generator=g, device=dev).to(torch.bfloat16)
+                h = torch.randn(rows, d, generator=gw, device=dev).to(torch.bfloat16)
+                w = torch.randn(d, generator=gw, device=dev).to(torch.bfloat16)
+                # the three separate steps
+                h_ref = h.clone()
+                want = add_rmsnorm(h_ref, peer.all_reduce(x).clone(), w, 1e-5)
+                # one kernel: all rows of the normalised result, own rows of h
+                h_own = h.clone()
+                got = peer.all_reduce_add_rmsnorm(x, h_own, w, 1e-5).clone()
+                assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (it, rows, d)
+                lo, hi = rank * rows // world, (rank + 1) * rows // world
+                assert torch.equal(h_own[lo:hi].view(torch.int16), h_ref[lo:hi].view(torch.int16))
+                other = torch.ones(rows, dtype=torch.bool)
+                other[lo:hi] = False
+                assert torch.equal(h_own[other].view(torch.int16), h[other].view(torch.int16))
+            # replayed from a graph behind the product that feeds it
+            coll = Collectives(None, peer)
+            a = torch.randn(64, 512, generator=g, device=dev).to(torch.bfloat16)
+            wt = torch.randn(1024, 512, generator=gw, device=dev).to(torch.bfloat16) * 0.05
+            wn = torch.randn(1024, generator=gw, device=dev).to(torch.bfloat16)
+            h = torch.zeros(64, 1024, device=dev, dtype=torch.bfloat16)
+            coll.linear_all_reduce_add_rmsnorm(a, wt, h, wn, 1e-5, True)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = coll.linear_all_reduce_add_rmsnorm(a, wt, h, wn, 1e-5, True)
+            for _ in range(10):
+                a.copy_(torch.randn(64, 512, generator=g, device=dev))
+                h.copy_(torch.randn(64, 1024, generator=gw, device=dev))
+                h_ref = h.clone()
+                graph.replay()
+                got = out.clone()  # the eager call below reuses the result buffers
+                want = coll.linear_all_reduce_add_rmsnorm(a, wt, h_ref, wn, 1e-5, False)
+                assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+            assert _lib.device_status(torch.cuda.current_stream().cuda_stream) == 0
+            torch.cuda.synchronize()
+            dist.barrier()
+            coll.close()
+        elif what == "decoder_fused":
+            from cwm_b200.decoder import DecoderArgs, DecodeState, ShardedDecoder
+
+            args = DecoderArgs(dim=256, n_layers=4, n_heads=4, n_kv_heads=2, head_dim=128,
+                               ffn_dim=512, vocab_size=1024, local_window=64, page_size=256)
+            logits = {}
+            for fuse in (False, True):
+                model = ShardedDecoder(args, rank, world, dev, seed=3, std=0.05,
+                                       peer_all_reduce=True, fuse_all_reduce=fuse)
+                cache = model.build_cache(8 * 256)
+                for c in cache.caches:
+                    c.copy_(torch.randn(c.shape, generator=torch.Generator().manual_seed(7 + rank))
+                            .to(torch.bfloat16))
+                table = torch.arange(8, dtype=torch.int32, device=dev).reshape(4, 2)
+                state = DecodeState(4, table, 256, dev)
+                state.copy_inputs(state.blktbl,
+                                  torch.tensor([5, 900, 33, 77], dtype=torch.int32, device=dev),
+                                  torch.tensor([100, 1, 400, 257], dtype=torch.int32, device=dev))
+                logits[fuse] = model.decode(state, cache).clone()
+                torch.cuda.synchronize()
+                dist.barrier()
+                model.coll.close()
+            # the fused kernel rounds where the separate steps round
+            assert torch.equal(logits[True], logits[False])
+            assert _lib.device_status(torch.cuda.current_stream().cuda_stream) == 0
         results[rank] = "ok"
     finally:
         torch.cuda.synchronize()
@@ -105,7 +176,8 @@ def _worker(rank: int, world: int, port: int, what: str, results) -> None:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("what", ["allreduce", "decoder"])
+@pytest.mark.parametrize("what", ["allreduce", "decoder", "allreduce_add_rmsnorm",
+                                  "decoder_fused"])
 def test_two_ranks(lib, what):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
